@@ -43,12 +43,12 @@ def registered_architectures():
 
 def _ensure_builtin():
     # Built-in architectures register themselves on import.
-    from ..models import llama  # noqa: F401
+    from ..models import kubedra, llama  # noqa: F401
 
 
 def resolve_architecture(config_dict) -> Architecture:
     _ensure_builtin()
-    names = config_dict.get("architectures") or []
+    names = config_dict.get("architectures") or config_dict.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for name in names:

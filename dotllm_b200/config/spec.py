@@ -64,10 +64,13 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers`` and may occur in several entries
     (shared weights).  ``cache_of`` is ``None`` when the execution keeps a cache
     of its own, or the index of an earlier schedule entry whose cache it reads
-    without writing.
+    without writing.  ``takes_embedding``: the embedding output (the stream as the
+    embedding left it) is added to the stream right before this execution (a
+    repeated run of layers that takes the input in again before each pass).
     """
     layer: int
     cache_of: Optional[int] = None
+    takes_embedding: bool = False
 
 
 @dataclass(frozen=True)

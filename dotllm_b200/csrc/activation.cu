@@ -2,6 +2,7 @@
 // Reference: native/kernels/swiglu_f32.cu:5-15 and the scalar CPU twin
 // src/DotLLM.Cpu/Kernels/FusedOps.cs:69-78 (sigmoid = 1 / (1 + exp(-g))).
 #include "common.cuh"
+#include "gating.cuh"
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -33,5 +34,40 @@ extern "C" int dl_swiglu(const void* gate, const void* up, int in_stride, void* 
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "swiglu: dtype %d", dtype);
     DL_CHECK_LAUNCH("swiglu");
+    return DL_OK;
+}
+
+// Other gatings of a feed-forward's two products, float32 arithmetic, chosen by `kind`:
+//   1  gelu_tanh(g) * u,  gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   2  g' sigmoid(alpha g') (u' + 1)  with g' = min(g, limit), u' = clamp(u, -limit, limit)
+// (kind 0 is the SwiGLU above.)  `limit` and `alpha` are parameters of kind 2.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_activation_kernel(const T* __restrict__ gate, const T* __restrict__ up, int in_stride, T* __restrict__ out,
+                        int rows, int width, int kind, float limit, float alpha) {
+    const size_t n = (size_t)rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width, c = i - r * width;
+        out[i] = dl_from_f32<T>(dl_gate_value(kind, dl_to_f32<T>(gate[r * in_stride + c]), dl_to_f32<T>(up[r * in_stride + c]),
+                                              limit, alpha));
+    }
+}
+
+extern "C" int dl_gated_activation(const void* gate, const void* up, int in_stride, void* out, int dtype, int rows,
+                                   int width, int kind, float limit, float alpha, void* stream) {
+    DL_REQUIRE(rows >= 0 && width > 0 && in_stride >= width && kind >= 0 && kind <= 2, "gated_activation: bad arguments");
+    if (rows == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)rows * width;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == DL_F32)
+        gated_activation_kernel<float><<<blocks, 256, 0, s>>>((const float*)gate, (const float*)up, in_stride, (float*)out,
+                                                              rows, width, kind, limit, alpha);
+    else if (dtype == DL_BF16)
+        gated_activation_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up,
+                                                                      in_stride, (__nv_bfloat16*)out, rows, width, kind, limit, alpha);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "gated_activation: dtype %d", dtype);
+    DL_CHECK_LAUNCH("gated_activation");
     return DL_OK;
 }

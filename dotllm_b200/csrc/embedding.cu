@@ -43,3 +43,39 @@ extern "C" int dl_gather_rows(const void* table, int dtype, int table_stride, co
     DL_CHECK_LAUNCH("gather_rows");
     return DL_OK;
 }
+
+// Token embedding plus a learned position vector: out[r, :] = table[ids[r], :] + positions[pos[r], :],
+// the sum in float32.  One block per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_positions_kernel(const T* __restrict__ table, const T* __restrict__ pos_table, const int32_t* __restrict__ ids,
+                       const int32_t* __restrict__ pos, float* __restrict__ out, int width, int n_table_rows,
+                       int n_positions) {
+    dl_launch_dependents();
+    const int row = blockIdx.x;
+    const int id = ids[row], p = pos[row];
+    float* dst = out + (size_t)row * width;
+    const bool ok = id >= 0 && id < n_table_rows && p >= 0 && p < n_positions;   // host-validated
+    const T* a = table + (size_t)(ok ? id : 0) * width;
+    const T* b = pos_table + (size_t)(ok ? p : 0) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = ok ? dl_to_f32<T>(a[c]) + dl_to_f32<T>(b[c]) : 0.f;
+}
+
+// table [n_table_rows, width], pos_table [n_positions, width] of `dtype`, both contiguous; out float32 [n_rows, width].
+extern "C" int dl_embed_positions(const void* table, const void* pos_table, int dtype, const int32_t* ids,
+                                  const int32_t* pos, float* out, int n_rows, int width, int n_table_rows,
+                                  int n_positions, void* stream) {
+    DL_REQUIRE(n_rows >= 0 && width > 0 && n_table_rows > 0 && n_positions > 0, "embed_positions: bad sizes");
+    if (n_rows == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DL_F32)
+        embed_positions_kernel<float><<<n_rows, 256, 0, s>>>((const float*)table, (const float*)pos_table, ids, pos, out, width,
+                                                             n_table_rows, n_positions);
+    else if (dtype == DL_BF16)
+        embed_positions_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table,
+                                                                     ids, pos, out, width, n_table_rows, n_positions);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "embed_positions: dtype %d", dtype);
+    DL_CHECK_LAUNCH("embed_positions");
+    return DL_OK;
+}

@@ -1,0 +1,203 @@
+// A feed-forward of many small experts of which every token uses a few.
+//
+//   router:  z = R x + b (float32);  the `top` largest z choose the experts, ties to the lower index;
+//            their weights are the softmax over the chosen z alone
+//   expert:  y = D_e act(G_e x, U_e x)       (act: one of the gatings of gating.cuh)
+//   output:  sum over the chosen experts of weight * y   (+ an addend per token, e.g. a shared expert)
+//
+// Three kernels, none of which needs the host to know which experts were chosen (a step can be
+// captured in a graph): the router (a warp per token), the gated product (a block per (token, chosen
+// expert) row, a warp per output: the row's activations wait in shared memory as float32 and every
+// lane walks its share of the expert's weight row), and the down product with the weighted sum in
+// it (a block per token).  Every output is one warp's sum in an order that depends only on the sizes,
+// so a token's result does not depend on what else is in the step.
+#include "common.cuh"
+#include "gating.cuh"
+
+#define EX_WARPS 8
+#define EX_OUT_PER_BLOCK 64
+
+template <typename T>
+__global__ void __launch_bounds__(32 * EX_WARPS)
+route_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ wr, const float* __restrict__ bias,
+                  int32_t* __restrict__ ids, float* __restrict__ weights, int rows, int K, int E, int top) {
+    extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * EX_WARPS + warp;
+    if (row >= rows) return;                          // warps are independent below
+    float* logits = route_smem + (size_t)warp * (E + top);
+    float* chosen = logits + E;
+    const T* xr = x + (size_t)row * x_stride;
+    for (int e = 0; e < E; ++e) {
+        const T* w = wr + (size_t)e * K;
+        float acc = 0.f;
+        for (int c = lane; c < K; c += 32) acc += dl_to_f32<T>(xr[c]) * dl_to_f32<T>(w[c]);
+        acc = dl_warp_sum(acc);
+        if (lane == 0) logits[e] = acc + (bias != nullptr ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int at = E;
+        for (int e = lane; e < E; e += 32) {
+            const float v = logits[e];
+            if (at == E || v > best) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa < E && (at == E || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            ids[(size_t)row * top + j] = at < E ? at : 0;
+            chosen[j] = best;
+            if (at < E) logits[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float m = chosen[0];
+        float sum = 0.f;
+        for (int j = 0; j < top; ++j) sum += expf(chosen[j] - m);
+        for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = expf(chosen[j] - m) / sum;
+    }
+}
+
+// x [rows, K] of dtype; wr [E, K] of dtype; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
+extern "C" int dl_route_topk(const void* x, int x_stride, const void* wr, const float* bias, int dtype, int32_t* ids,
+                             float* weights, int rows, int K, int E, int top, void* stream) {
+    DL_REQUIRE(rows >= 0 && K > 0 && E > 0 && top > 0 && top <= E && x_stride >= K, "route_topk: bad sizes E=%d top=%d", E, top);
+    const size_t smem = (size_t)EX_WARPS * (E + top) * sizeof(float);
+    DL_REQUIRE(smem <= 48 * 1024, "route_topk: %d experts are more than the kernel's shared memory takes", E);
+    if (rows == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((rows + EX_WARPS - 1) / EX_WARPS), block(32 * EX_WARPS);
+    cudaError_t e;
+    if (dtype == DL_F32)
+        e = dl_launch_dependent(route_topk_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, (const float*)wr, bias,
+                                ids, weights, rows, K, E, top);
+    else if (dtype == DL_BF16)
+        e = dl_launch_dependent(route_topk_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride,
+                                (const __nv_bfloat16*)wr, bias, ids, weights, rows, K, E, top);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "route_topk: dtype %d", dtype);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "route_topk: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
+// Row r = (token r / top, chosen expert ids[r]):  out[r, n] = act(G_e[n, :] . x[token], U_e[n, :] . x[token]).
+// w: [E, 2 * ff, K], an expert's gate rows first, then its up rows.
+template <typename T>
+__global__ void __launch_bounds__(32 * EX_WARPS)
+expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __restrict__ ids, const T* __restrict__ w,
+                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha) {
+    extern __shared__ float ex_x[];                  // [K]
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* xr = x + (size_t)(r / top) * x_stride;
+    for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[c] = dl_to_f32<T>(xr[c]);
+    __syncthreads();
+    const int e = ids[r];
+    const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
+    const int n1 = min(ff, n0 + EX_OUT_PER_BLOCK);
+    const bool ok = e >= 0 && e < E;
+    const T* we = w + (size_t)(ok ? e : 0) * 2 * ff * K;
+    for (int n = n0 + warp; n < n1; n += EX_WARPS) {
+        const T* gr = we + (size_t)n * K;
+        const T* ur = we + (size_t)(ff + n) * K;
+        float g = 0.f, u = 0.f;
+        for (int c = lane; c < K; c += 32) {
+            const float xv = ex_x[c];
+            g += xv * dl_to_f32<T>(gr[c]);
+            u += xv * dl_to_f32<T>(ur[c]);
+        }
+        g = dl_warp_sum(g);
+        u = dl_warp_sum(u);
+        if (lane == 0) out[(size_t)r * ff + n] = dl_from_f32<T>(ok ? dl_gate_value(kind, g, u, limit, alpha) : 0.f);
+    }
+}
+
+extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids, const void* w, void* out, int dtype,
+                                 int tokens, int top, int K, int ff, int E, int kind, float limit, float alpha, void* stream) {
+    DL_REQUIRE(tokens >= 0 && top > 0 && K > 0 && ff > 0 && E > 0 && x_stride >= K && kind >= 0 && kind <= 2,
+               "expert_gate_up: bad arguments");
+    DL_REQUIRE((size_t)K * sizeof(float) <= 48 * 1024, "expert_gate_up: rows of %d values are more than the kernel takes", K);
+    if (tokens == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(tokens * top, (ff + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
+    const size_t smem = (size_t)K * sizeof(float);
+    cudaError_t e;
+    if (dtype == DL_F32)
+        e = dl_launch_dependent(expert_gate_up_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, ids, (const float*)w,
+                                (float*)out, top, K, ff, E, kind, limit, alpha);
+    else if (dtype == DL_BF16)
+        e = dl_launch_dependent(expert_gate_up_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride, ids,
+                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "expert_gate_up: dtype %d", dtype);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gate_up: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
+// out[t, n] = sum_j weights[t, j] * (D_e(t,j)[n, :] . h[t * top + j, :])  (+ addend[t, n]), float32.
+// h: [tokens * top, ff] of dtype; w: [E, N, ff].
+template <typename T>
+__global__ void __launch_bounds__(32 * EX_WARPS)
+expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                   const T* __restrict__ w, const float* __restrict__ addend, int addend_stride, float* __restrict__ out,
+                   int top, int ff, int N, int E) {
+    extern __shared__ float ex_h[];                  // [top][ff]
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* hr = h + (size_t)t * top * ff;
+    for (int c = threadIdx.x; c < top * ff; c += blockDim.x) ex_h[c] = dl_to_f32<T>(hr[c]);
+    __syncthreads();
+    const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
+    const int n1 = min(N, n0 + EX_OUT_PER_BLOCK);
+    for (int n = n0 + warp; n < n1; n += EX_WARPS) {
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = ids[(size_t)t * top + j];
+            if (e < 0 || e >= E) continue;
+            const T* wr = w + ((size_t)e * N + n) * ff;
+            const float* hj = ex_h + (size_t)j * ff;
+            float acc = 0.f;
+            for (int c = lane; c < ff; c += 32) acc += hj[c] * dl_to_f32<T>(wr[c]);
+            acc = dl_warp_sum(acc);
+            total += weights[(size_t)t * top + j] * acc;
+        }
+        if (lane == 0) out[(size_t)t * N + n] = total + (addend != nullptr ? addend[(size_t)t * addend_stride + n] : 0.f);
+    }
+}
+
+extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* weights, const void* w, const float* addend,
+                              int addend_stride, float* out, int dtype, int tokens, int top, int ff, int N, int E,
+                              void* stream) {
+    DL_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && N > 0 && E > 0, "expert_down: bad sizes");
+    DL_REQUIRE((size_t)top * ff * sizeof(float) <= 96 * 1024, "expert_down: %d x %d activations are more than the kernel takes", top, ff);
+    if (tokens == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(tokens, (N + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
+    const size_t smem = (size_t)top * ff * sizeof(float);
+    cudaError_t e;
+    if (dtype == DL_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = dl_launch_dependent(expert_down_kernel<float>, grid, block, smem, s, (const float*)h, ids, weights, (const float*)w,
+                                addend, addend_stride, out, top, ff, N, E);
+    } else if (dtype == DL_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(expert_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = dl_launch_dependent(expert_down_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, ids, weights,
+                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E);
+    } else
+        return dl_fail(DL_ERR_UNSUPPORTED, "expert_down: dtype %d", dtype);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));
+    return DL_OK;
+}

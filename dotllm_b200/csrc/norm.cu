@@ -142,3 +142,125 @@ extern "C" int dl_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     if (!df && of) return launch_norm<__nv_bfloat16, float>(residual, delta, gain, out, rows, width, eps, s);
     return launch_norm<__nv_bfloat16, __nv_bfloat16>(residual, delta, gain, out, rows, width, eps, s);
 }
+
+// A branch output that is normalised before it joins the stream (a layer with a norm behind each
+// sublayer as well as before it), fused with the norm that follows:
+//
+//   residual += delta / sqrt(mean(delta^2) + delta_eps) * delta_gain  (+ extra)
+//   out       = residual / sqrt(mean(residual^2) + eps) * gain          (when out is given)
+//
+// One block per row, float32 statistics, a fixed order of additions per row.  `extra` (float32, same
+// shape as the stream, or NULL) is added as it is: the embedding output that a repeated group of
+// layers takes in again before each pass.  Rows of up to 4 * NORM_THREADS values keep the sum in
+// registers between the passes; wider rows go through the stream in memory.
+#define BRANCH_MAX 4
+
+template <typename TDelta, typename TOut>
+__global__ void __launch_bounds__(NORM_THREADS)
+branch_norm_add_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta, int delta_stride,
+                       const float* __restrict__ delta_gain, float delta_eps, const float* __restrict__ extra,
+                       const float* __restrict__ gain, TOut* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[33];
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * width;
+    const TDelta* drow = delta + (size_t)blockIdx.x * delta_stride;
+    const bool in_regs = width <= BRANCH_MAX * NORM_THREADS;
+    float d[BRANCH_MAX];
+    float ssd = 0.f;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < BRANCH_MAX; ++i) {
+            const int c = threadIdx.x + i * NORM_THREADS;
+            d[i] = c < width ? dl_to_f32<TDelta>(drow[c]) : 0.f;
+            ssd += d[i] * d[i];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += NORM_THREADS) {
+            const float v = dl_to_f32<TDelta>(drow[c]);
+            ssd += v * v;
+        }
+    }
+    ssd = dl_block_sum(ssd, scratch);
+    const float dscale = 1.0f / sqrtf(ssd / (float)width + delta_eps);
+    float ss = 0.f;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < BRANCH_MAX; ++i) {
+            const int c = threadIdx.x + i * NORM_THREADS;
+            if (c < width) {
+                float v = residual[base + c] + d[i] * dscale * delta_gain[c];
+                if (extra != nullptr) v += extra[base + c];
+                residual[base + c] = v;
+                d[i] = v;
+                ss += v * v;
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += NORM_THREADS) {
+            float v = residual[base + c] + dl_to_f32<TDelta>(drow[c]) * dscale * delta_gain[c];
+            if (extra != nullptr) v += extra[base + c];
+            residual[base + c] = v;
+            ss += v * v;
+        }
+    }
+    if (out == nullptr) return;
+    ss = dl_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < BRANCH_MAX; ++i) {
+            const int c = threadIdx.x + i * NORM_THREADS;
+            if (c < width) out[base + c] = dl_from_f32<TOut>(d[i] * scale * gain[c]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += NORM_THREADS)
+            out[base + c] = dl_from_f32<TOut>(residual[base + c] * scale * gain[c]);
+    }
+}
+
+template <typename TDelta, typename TOut>
+static int launch_branch(float* residual, const void* delta, int delta_stride, const float* delta_gain, float delta_eps,
+                         const float* extra, const float* gain, void* out, int rows, int width, float eps, cudaStream_t s) {
+    cudaError_t e = dl_launch_dependent(branch_norm_add_kernel<TDelta, TOut>, dim3(rows), dim3(NORM_THREADS), 0, s, residual,
+                                        (const TDelta*)delta, delta_stride, delta_gain, delta_eps, extra, gain, (TOut*)out,
+                                        width, eps);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "branch_norm_add: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
+// residual float32 [rows, width] contiguous, updated in place; delta [rows, width] of delta_dtype, rows
+// delta_stride elements apart; delta_gain, gain float32 [width]; extra float32 [rows, width] or NULL;
+// out [rows, width] of out_dtype or NULL (then gain may be NULL too: the stream is only added to).
+extern "C" int dl_branch_norm_add(float* residual, const void* delta, int delta_dtype, int delta_stride,
+                                  const float* delta_gain, float delta_eps, const float* extra, const float* gain,
+                                  void* out, int out_dtype, int rows, int width, float eps, void* stream) {
+    DL_REQUIRE(rows >= 0 && width > 0 && delta_stride >= width, "branch_norm_add: bad sizes rows=%d width=%d", rows, width);
+    DL_REQUIRE(delta_eps > 0.f && (out == nullptr || (eps > 0.f && gain != nullptr)), "branch_norm_add: eps must be positive");
+    if (rows == 0) return DL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool df = (delta_dtype == DL_F32), of = (out_dtype == DL_F32);
+    DL_REQUIRE(df || delta_dtype == DL_BF16, "branch_norm_add: delta dtype %d", delta_dtype);
+    DL_REQUIRE(of || out_dtype == DL_BF16, "branch_norm_add: out dtype %d", out_dtype);
+    if (df && of) return launch_branch<float, float>(residual, delta, delta_stride, delta_gain, delta_eps, extra, gain, out, rows, width, eps, s);
+    if (df && !of) return launch_branch<float, __nv_bfloat16>(residual, delta, delta_stride, delta_gain, delta_eps, extra, gain, out, rows, width, eps, s);
+    if (!df && of) return launch_branch<__nv_bfloat16, float>(residual, delta, delta_stride, delta_gain, delta_eps, extra, gain, out, rows, width, eps, s);
+    return launch_branch<__nv_bfloat16, __nv_bfloat16>(residual, delta, delta_stride, delta_gain, delta_eps, extra, gain, out, rows, width, eps, s);
+}
+
+// Stream += other, float32, elementwise (a stream that takes another in when no norm follows at once).
+__global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) a[i] += b[i];
+}
+
+extern "C" int dl_add_rows(float* a, const float* b, int rows, int width, void* stream) {
+    DL_REQUIRE(rows >= 0 && width > 0, "add_rows: bad sizes");
+    if (rows == 0) return DL_OK;
+    const size_t n = (size_t)rows * width;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    cudaError_t e = dl_launch_dependent(add_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, a, b, n);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "add_rows: %s", cudaGetErrorString(e));
+    return DL_OK;
+}

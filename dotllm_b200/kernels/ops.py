@@ -13,6 +13,18 @@ from . import attention_fast, gemm_skinny, gemm_tc
 from . import library as _library
 
 PAGE = 64                      # tokens per cache page (DL_PAGE in csrc/common.cuh)
+_P, _I, _F = _library._P, _library._I, _library._F
+_library.register_signatures({
+    "dl_embed_positions": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "dl_branch_norm_add": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _I, _I, _I, _F, _P],
+    "dl_add_rows": [_P, _P, _I, _I, _P],
+    "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
+    "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "dl_route_topk": [_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+})
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 
@@ -72,6 +84,24 @@ def gather_rows(table, ids, out=None, out_dtype=torch.float32):
     return out
 
 
+def embed_positions(table, pos_table, ids, positions):
+    """out[r] = table[ids[r]] + pos_table[positions[r]] in float32.  Both tables [n, width] contiguous
+    and of one dtype; ids, positions int32 [R]."""
+    _need_cuda(table, pos_table, ids, positions)
+    if table.dim() != 2 or pos_table.dim() != 2 or table.shape[1] != pos_table.shape[1] or table.dtype != pos_table.dtype \
+            or not table.is_contiguous() or not pos_table.is_contiguous():
+        raise KernelError("embed_positions: need two contiguous tables of one dtype and one width")
+    _int32(ids, "embed_positions ids")
+    _int32(positions, "embed_positions positions")
+    rows = ids.numel()
+    if positions.numel() != rows:
+        raise KernelError("embed_positions: one position per id")
+    out = torch.empty((rows, table.shape[1]), dtype=torch.float32, device=table.device)
+    _library.call("dl_embed_positions", _ptr(table), _ptr(pos_table), _code(table.dtype), _ptr(ids), _ptr(positions),
+                  _ptr(out), rows, table.shape[1], table.shape[0], pos_table.shape[0], _stream())
+    return out
+
+
 # ------------------------------------------------- products not yet launched
 class PendingProduct:
     """x W^T (float32 result of bfloat16 operands) that ``linear(..., lazy=True)`` has not launched
@@ -119,9 +149,32 @@ class ScaledRows:
         return add_rmsnorm(self.stream, None, self.gain, self.eps, self.data.dtype)
 
 
+class NormedBranch:
+    """A branch output that joins the stream only after a norm of its own: ``data`` [T, H] (float32 or
+    bfloat16, or a product not yet launched) is divided by its rows' root mean square (``eps`` inside
+    the root) and multiplied by ``gain`` before the addition.  ``extra`` (float32 [T, H] or None) is
+    added to the stream as it is at the same time.  ``add_rmsnorm`` takes it as the delta and does
+    norm, addition and the next norm in one kernel."""
+
+    def __init__(self, data, gain, eps, extra=None):
+        self.data, self.gain, self.eps, self.extra = data, gain, float(eps), extra
+        self.shape = tuple(data.shape)
+
+    def with_extra(self, extra):
+        if self.extra is not None:
+            raise KernelError("a normed branch takes one extra addend")
+        return NormedBranch(self.data, self.gain, self.eps, extra)
+
+    def tensor(self):
+        """The normalised branch (and the extra addend) as one float32 tensor."""
+        out = torch.zeros(self.shape, dtype=torch.float32, device=self.gain.device)
+        add_normed_branch(out, self)
+        return out
+
+
 def resolve(value):
-    """The tensor behind a PendingProduct or ScaledRows; tensors and None pass through."""
-    return value.tensor() if isinstance(value, (PendingProduct, ScaledRows)) else value
+    """The tensor behind a PendingProduct, ScaledRows or NormedBranch; tensors and None pass through."""
+    return value.tensor() if isinstance(value, (PendingProduct, ScaledRows, NormedBranch)) else value
 
 
 def narrow_rows(value, ids):
@@ -132,6 +185,9 @@ def narrow_rows(value, ids):
     if isinstance(value, PendingProduct):
         x = resolve(value.x)
         return PendingProduct(gather_rows(x, ids, out_dtype=x.dtype), value.w, value.resident)
+    if isinstance(value, NormedBranch):
+        return NormedBranch(narrow_rows(value.data, ids), value.gain, value.eps,
+                            None if value.extra is None else gather_rows(value.extra, ids))
     value = resolve(value)
     return gather_rows(value, ids, out_dtype=value.dtype)
 
@@ -144,6 +200,8 @@ def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
     PendingProduct, or None.  gain: float32 [H].  ``lazy``: the caller will hand the result straight
     to ``linear`` / ``gated_linear``, so it may be a ScaledRows: a pending product then does the
     addition itself and the next product the normalisation, with no kernel in between."""
+    if isinstance(delta, NormedBranch):
+        return add_normed_branch(residual, delta, gain, eps, out_dtype)
     if isinstance(delta, PendingProduct):
         fused = _add_product_scaled(residual, delta, gain, eps, out_dtype) if lazy else None
         if fused is not None:
@@ -162,6 +220,40 @@ def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
                   _code(delta.dtype) if delta is not None else 0, _ptr(gain), _ptr(out),
                   _code(out_dtype), rows, width, float(eps), _stream())
     return out
+
+
+def add_normed_branch(residual, branch, gain=None, eps=0.0, out_dtype=None):
+    """residual += rmsnorm(branch.data) * branch.gain (+ branch.extra), in place; with ``gain`` also returns
+    rmsnorm(residual) * gain in ``out_dtype`` (one kernel), else None."""
+    data = resolve(branch.data)
+    _need_cuda(residual, data, branch.gain, branch.extra, gain)
+    if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
+        raise KernelError("normed branch: the residual stream must be contiguous float32 [T, H]")
+    rows, width = residual.shape
+    stride = _rows_view(data, "normed branch")
+    if tuple(data.shape) != (rows, width):
+        raise KernelError(f"normed branch: a branch of shape {tuple(data.shape)} does not fit a stream of {(rows, width)}")
+    for g in (branch.gain, gain):
+        if g is not None and (g.dtype != torch.float32 or g.shape != (width,) or not g.is_contiguous()):
+            raise KernelError(f"normed branch: gains must be float32 [{width}]")
+    extra = branch.extra
+    if extra is not None and (extra.dtype != torch.float32 or tuple(extra.shape) != (rows, width) or not extra.is_contiguous()):
+        raise KernelError("normed branch: the extra addend must be contiguous float32 with the stream's shape")
+    out = torch.empty((rows, width), dtype=out_dtype, device=residual.device) if gain is not None else None
+    _library.call("dl_branch_norm_add", _ptr(residual), _ptr(data), _code(data.dtype), stride, _ptr(branch.gain),
+                  branch.eps, _ptr(extra), _ptr(gain), _ptr(out), _code(out_dtype) if out is not None else 0, rows, width,
+                  float(eps), _stream())
+    return out
+
+
+def add_rows(residual, other):
+    """residual += other, both contiguous float32 of one shape, in place."""
+    _need_cuda(residual, other)
+    if residual.dtype != torch.float32 or other.dtype != torch.float32 or residual.shape != other.shape \
+            or residual.dim() != 2 or not residual.is_contiguous() or not other.is_contiguous():
+        raise KernelError("add_rows: need two contiguous float32 tensors of one shape")
+    _library.call("dl_add_rows", _ptr(residual), _ptr(other), residual.shape[0], residual.shape[1], _stream())
+    return residual
 
 
 def _add_product_scaled(residual, product, gain, eps, out_dtype):
@@ -341,7 +433,152 @@ def swiglu(gate_up):
     return out
 
 
+GATINGS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
+
+
+def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
+    """act(gate, up) for gate_up = [gate | up] of shape [T, 2I]; returns [T, I].  ``kind``: "silu"
+    (g sigmoid(g) u), "gelu_tanh" (tanh form of gelu(g), times u) or "clamped_sigmoid"
+    (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit))."""
+    _need_cuda(gate_up)
+    if kind not in GATINGS:
+        raise KernelError(f"gated_activation: unknown gating {kind!r}; known: {sorted(GATINGS)}")
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise KernelError("gated_activation: need a contiguous [T, 2I] tensor")
+    rows, two_i = gate_up.shape
+    width = two_i // 2
+    out = torch.empty((rows, width), dtype=gate_up.dtype, device=gate_up.device)
+    _library.call("dl_gated_activation", gate_up.data_ptr(), gate_up.data_ptr() + width * gate_up.element_size(), two_i,
+                  _ptr(out), _code(gate_up.dtype), rows, width, GATINGS[kind], float(limit), float(alpha), _stream())
+    return out
+
+
+# ------------------------------------------------------- gated linear attention
+def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau):
+    """The recurrence S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t q_scale) with
+    alpha_t = sigmoid(z_t + z_bias)^(1/tau), over each sequence's new rows in order, from and into
+    ``state`` float32 [slots, H, dim, vdim].  q, k [T, H*dim] and v [T, H*vdim] are column views of one
+    matrix (a common row stride) and of one dtype, z float32 [T, H*dim].  Returns o float32 [T, H*vdim]."""
+    _need_cuda(q, k, v, z, z_bias, cu_new, slots, state)
+    T = q.shape[0]
+    ld = _rows_view(q, "gla q")
+    if _rows_view(k, "gla k") != ld or _rows_view(v, "gla v") != ld or k.shape != (T, n_heads * dim) \
+            or q.shape != k.shape or v.shape != (T, n_heads * vdim) or z.shape != k.shape:
+        raise KernelError("gla_scan: q, k, v must be column views of one matrix, z [T, H*dim]")
+    if not (q.dtype == k.dtype == v.dtype) or z.dtype != torch.float32:
+        raise KernelError("gla_scan: q, k and v must share one dtype and z be float32")
+    zs = _rows_view(z, "gla z")
+    if z_bias.dtype != torch.float32 or z_bias.shape != (n_heads * dim,) or not z_bias.is_contiguous():
+        raise KernelError("gla_scan: the decay bias must be float32 [H*dim]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
+        raise KernelError("gla_scan: the state must be contiguous float32 [slots, H, dim, vdim]")
+    _int32(cu_new, "gla cu_new")
+    _int32(slots, "gla slots")
+    out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=q.device)
+    _library.call("dl_gla_scan", _ptr(q), _ptr(k), _ptr(v), ld, _ptr(z), zs, _ptr(z_bias), _code(q.dtype), _ptr(cu_new),
+                  _ptr(slots), _ptr(state), state.shape[0], _ptr(out), out.stride(0), slots.numel(), n_heads, dim, vdim,
+                  float(q_scale), float(tau), _stream())
+    return out
+
+
+def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
+    """Each head's rows of o (float32 [T, H*vdim]) divided by their root mean square, times ``gain``
+    (float32 [vdim], shared by the heads), times silu(g) (g [T, H*vdim] of ``out_dtype``, a column view is fine)."""
+    _need_cuda(o, g, gain)
+    T = o.shape[0]
+    gs = _rows_view(g, "head_norm_gate g")
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape != (T, n_heads * vdim) or g.shape != o.shape \
+            or g.dtype != out_dtype or gain.dtype != torch.float32 or gain.shape != (vdim,) or not gain.is_contiguous():
+        raise KernelError("head_norm_gate: o float32 [T, H*vdim], g of the output's dtype and shape, gain float32 [vdim]")
+    out = torch.empty((T, n_heads * vdim), dtype=out_dtype, device=o.device)
+    _library.call("dl_head_norm_gate", _ptr(o), o.stride(0), _ptr(g), gs, _ptr(gain), _ptr(out), out.stride(0),
+                  _code(out_dtype), T, n_heads, vdim, float(eps), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- experts
+def route_topk(x, w_router, bias, top):
+    """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and the
+    softmax over the chosen logits alone.  Returns (ids int32 [T, top], weights float32 [T, top])."""
+    _need_cuda(x, w_router, bias)
+    xs = _rows_view(x, "route x")
+    E, K = w_router.shape
+    if x.shape[1] != K or x.dtype != w_router.dtype or not w_router.is_contiguous():
+        raise KernelError(f"route_topk: x {tuple(x.shape)} does not match the router {tuple(w_router.shape)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (E,) or not bias.is_contiguous()):
+        raise KernelError(f"route_topk: the bias must be float32 [{E}]")
+    if not 0 < top <= E:
+        raise KernelError(f"route_topk: cannot choose {top} of {E} experts")
+    T = x.shape[0]
+    ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    _library.call("dl_route_topk", _ptr(x), xs, _ptr(w_router), _ptr(bias), _code(x.dtype), _ptr(ids), _ptr(weights),
+                  T, K, E, top, _stream())
+    return ids, weights
+
+
+def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0):
+    """Row (t, j) = act(G_e x_t, U_e x_t) for e = ids[t, j].  x [T, K]; w_gate_up [E, 2*ff, K] (an expert's gate
+    rows, then its up rows); returns [T*top, ff] in x's dtype."""
+    _need_cuda(x, ids, w_gate_up)
+    xs = _rows_view(x, "expert x")
+    _int32(ids, "expert ids")
+    if w_gate_up.dim() != 3 or not w_gate_up.is_contiguous() or w_gate_up.shape[1] % 2 or w_gate_up.shape[2] != x.shape[1] \
+            or w_gate_up.dtype != x.dtype or ids.dim() != 2 or ids.shape[0] != x.shape[0]:
+        raise KernelError("expert_gate_up: x [T, K], ids [T, top], weights [E, 2*ff, K] of x's dtype")
+    E, two_ff, K = w_gate_up.shape
+    T, top = ids.shape
+    out = torch.empty((T * top, two_ff // 2), dtype=x.dtype, device=x.device)
+    _library.call("dl_expert_gate_up", _ptr(x), xs, _ptr(ids), _ptr(w_gate_up), _ptr(out), _code(x.dtype), T, top, K,
+                  two_ff // 2, E, GATINGS[kind], float(limit), float(alpha), _stream())
+    return out
+
+
+def expert_down(h, ids, weights, w_down, addend=None):
+    """out[t] = sum_j weights[t, j] * D_e(t,j) h[t*top + j]  (+ addend[t]), float32 [T, N].  h [T*top, ff];
+    w_down [E, N, ff] of h's dtype; addend float32 [T, N] (rows contiguous) or None."""
+    _need_cuda(h, ids, weights, w_down, addend)
+    _int32(ids, "expert ids")
+    T, top = ids.shape
+    if w_down.dim() != 3 or not w_down.is_contiguous() or w_down.dtype != h.dtype or not h.is_contiguous() \
+            or h.shape != (T * top, w_down.shape[2]) or weights.dtype != torch.float32 or weights.shape != ids.shape \
+            or not weights.is_contiguous():
+        raise KernelError("expert_down: h [T*top, ff], ids and float32 weights [T, top], matrices [E, N, ff] of h's dtype")
+    E, N, ff = w_down.shape
+    astride = 0
+    if addend is not None:
+        astride = _rows_view(addend, "expert addend")
+        if addend.dtype != torch.float32 or addend.shape != (T, N):
+            raise KernelError("expert_down: the addend must be float32 [T, N]")
+    out = torch.empty((T, N), dtype=torch.float32, device=h.device)
+    _library.call("dl_expert_down", _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_down), _ptr(addend), astride, _ptr(out),
+                  _code(h.dtype), T, top, ff, N, E, _stream())
+    return out
+
+
 # --------------------------------------------------------------------- linear
+def linear_per_head(x, w):
+    """y[t, h, :] = W[h] x[t, h, :] for x [T, H*a] (rows contiguous) and W [H, b, a]; returns [T, H*b] in x's dtype.
+    bfloat16: one batched library product with float32 accumulation; float32: the FFMA product head by head."""
+    _need_cuda(x, w)
+    if w.dim() != 3 or not w.is_contiguous() or x.dim() != 2 or x.shape[1] != w.shape[0] * w.shape[2] or x.dtype != w.dtype:
+        raise KernelError(f"linear_per_head: x {tuple(x.shape)} does not match W {tuple(w.shape)}")
+    H, b, a = w.shape
+    T = x.shape[0]
+    xs = _rows_view(x, "linear_per_head x")
+    y = torch.empty((T, H * b), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return y
+    if x.dtype == torch.float32:
+        for h in range(H):
+            _library.call("dl_gemm_f32", x.data_ptr() + 4 * h * a, xs, w[h].data_ptr(), y.data_ptr() + 4 * h * b, H * b,
+                          T, b, a, _stream())
+        return y
+    xv = x.as_strided((H, T, a), (a, xs, 1))
+    torch.bmm(xv, w.transpose(1, 2), out=y.view(T, H, b).transpose(0, 1))
+    return y
+
+
 def linear(x, w, out_dtype=None, resident=False, lazy=False):
     """y = x W^T for W [N, K].  ``resident``: the caller vouches that nothing still pending on the
     stream writes W (a model's weights), which lets the decode kernel start streaming W while

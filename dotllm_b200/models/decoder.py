@@ -102,6 +102,8 @@ class DecoderModel:
         """Logits float32 [wanted rows, vocab] of one step (see engine.step)."""
         residual = self.embedding.forward(step)
         pending = None
+        # the embedding output, for executions that take it in again (the stream itself is updated in place)
+        embedded = residual.clone() if any(e.takes_embedding for e in self.spec.schedule) else None
         # Logits are wanted at some rows only (a prompt's last token): the last layer in the order of
         # running still caches every token, but may hand on the wanted rows alone.
         some = 0 < step.n_wanted and not step.want_all
@@ -110,6 +112,11 @@ class DecoderModel:
         for e, entry in enumerate(self.spec.schedule):
             view = cache.view(e, step.block_tables, step.slots)
             block = self.blocks[entry.layer]
+            if entry.takes_embedding:
+                if isinstance(pending, ops.NormedBranch) and pending.extra is None:
+                    pending = pending.with_extra(embedded)        # rides the kernel that adds the branch
+                else:
+                    ops.add_rows(residual, embedded)
             if e == last and some and block.narrows:
                 residual, pending = block.forward(residual, pending, step, view, keep_rows=step.want_rows)
                 narrowed = True

@@ -42,10 +42,13 @@ class WeightSpec:
     role "index": integer table; kept as int32.
     ``init`` says how the random-weights mode fills it: ("normal", std), ("ones",),
     ("one_plus_uniform", a) or ("zeros",).
+    ``free_dims``: dimensions whose size only the stored tensor gives (a rank that no configuration
+    key names); ``shape`` holds the size the random-weights mode uses there, a checkpoint may hold any.
     """
     shape: tuple
     role: str = "matrix"
     init: tuple = ("normal", 0.02)
+    free_dims: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -124,6 +127,11 @@ class Norm(Part):
 
     def add_forward(self, residual, delta):
         """residual += delta in place (float32), then the normalised result in the run dtype."""
+        raise NotImplementedError
+
+    def branch(self, data):
+        """``data`` (a branch output) as something that joins the stream only after this norm: what a
+        layer with a norm behind each sublayer hands on as its pending branch (``ops.NormedBranch``)."""
         raise NotImplementedError
 
 
@@ -255,7 +263,8 @@ def registered(family):
 
 
 def _ensure_builtin():
-    from . import norms, rotary, attention, feed_forward, blocks, embedding  # noqa: F401
+    from . import (norms, rotary, attention, feed_forward, blocks, embedding, linear_attention,  # noqa: F401
+                   latent_attention, experts)
 
 
 def make_part(family, spec, hidden_size, runtime):

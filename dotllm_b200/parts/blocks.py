@@ -28,4 +28,26 @@ class PreNormBlock(Arrangement):
         return residual, self.feed_forward.forward(n)
 
 
+class SandwichNormBlock(Arrangement):
+    """A norm before and behind each sublayer: h += post(mixer(pre(h))); h += post(ff(pre(h))).  The
+    feed-forward and its two norms may be absent (a layer that only mixes).  A sublayer's output is handed
+    on with its post-norm still to be applied (``Norm.branch``): the norm that reads the stream next
+    normalises the branch, adds it and normalises the sum in one kernel, across the layer boundary too."""
+    needs = ("mixer_norm", "mixer", "mixer_post_norm")
+    narrows = True
+
+    def forward(self, residual, pending, step, cache_view, keep_rows=None):
+        n = normalised_for(self.mixer, self.mixer_norm, residual, pending)
+        branch = self.mixer_post_norm.branch(self.mixer.forward(n, step, cache_view))
+        if keep_rows is not None:
+            from ..kernels import ops
+            residual = ops.gather_rows(residual, keep_rows)
+            branch = ops.narrow_rows(branch, keep_rows)
+        if "feed_forward" not in self.parts:
+            return residual, branch
+        n = normalised_for(self.feed_forward, self.feed_forward_norm, residual, branch)
+        return residual, self.feed_forward_post_norm.branch(self.feed_forward.forward(n))
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("sandwich_norm", SandwichNormBlock)

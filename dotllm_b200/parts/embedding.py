@@ -34,6 +34,31 @@ class TokenEmbedding(Part):
         return ops.gather_rows(self.table, step.tokens)
 
 
+class TokenPositionEmbedding(Part):
+    """Token embedding plus a learned vector per absolute position, neither scaled: h[t] = E[token] + P[pos].
+    params: ``vocab_size``, ``max_positions``; optional ``token_tensor`` / ``position_tensor`` (local names,
+    default "weight" and "positions.weight")."""
+
+    def __init__(self, params, hidden_size, runtime):
+        super().__init__(params, hidden_size, runtime)
+        self.vocab_size = int(params["vocab_size"])
+        self.max_positions = int(params["max_positions"])
+        self.token_name = str(params.get("token_tensor", "weight"))
+        self.position_name = str(params.get("position_tensor", "positions.weight"))
+        self.table = self.positions = None
+
+    def weight_specs(self):
+        return {self.token_name: WeightSpec((self.vocab_size, self.hidden_size)),
+                self.position_name: WeightSpec((self.max_positions, self.hidden_size))}
+
+    def bind(self, tensors):
+        self.table = tensors[self.token_name].contiguous()
+        self.positions = tensors[self.position_name].contiguous()
+
+    def forward(self, step):
+        return ops.embed_positions(self.table, self.positions, step.tokens, step.token_pos)
+
+
 class LinearHead(Part):
     """params: ``vocab_size``.  Whether its matrix is the embedding table is the model description's
     business (``ModelSpec.shared_weights``): the part is handed a [vocab, hidden] matrix either way."""
@@ -61,4 +86,5 @@ class LinearHead(Part):
 
 
 register_embedding("token_embedding", TokenEmbedding)
+register_embedding("token_position_embedding", TokenPositionEmbedding)
 register_head("linear_head", LinearHead)

@@ -1,0 +1,96 @@
+"""A feed-forward of many small gated experts, a few per token, with an optional expert that every token uses.
+
+    z = R x + b (float32);  chosen = the ``top`` largest z;  weights = softmax over the chosen z alone
+    y = sum over chosen e of weight_e * D_e act(G_e x, U_e x)   (+ Ds act(Gs x, Us x), the shared expert)
+
+Router, choice, the experts' products and the weighted sum are kernels that read the choice on the device,
+so a step with this part can be captured in a graph.  The experts' matrices are stacked when the weights are
+bound ([E, 2*ff, H] gate rows then up rows, and [E, H, ff]).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..errors import ConfigError
+from ..kernels import ops
+from .base import FeedForward, WeightSpec, register_feed_forward
+
+
+class RoutedExperts(FeedForward):
+    """params: ``n_experts``, ``top``, ``intermediate_size`` (of one expert), ``activation`` (one of
+    ``ops.GATINGS``) with ``limit`` and ``alpha``; ``router_bias`` (default True); ``shared``: None or
+    {"intermediate_size", "limit"} (same activation and alpha); optional ``tensors``: local name patterns
+    ``expert`` (with {e} and {m} for the expert's index and gate / up / down), ``router``, ``router_bias``,
+    ``shared`` (with {m})."""
+
+    NAMES = {"expert": "experts.{e}.{m}_proj.weight", "router": "router.weight", "router_bias": "router.bias",
+             "shared": "shared_expert.{m}_proj.weight"}
+
+    def __init__(self, params, hidden_size, runtime):
+        super().__init__(params, hidden_size, runtime)
+        self.n_experts = int(params["n_experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["intermediate_size"])
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.GATINGS:
+            raise ConfigError(f"routed experts: unsupported activation {self.activation!r}; known: {sorted(ops.GATINGS)}")
+        if not 0 < self.top <= self.n_experts or self.ff <= 0:
+            raise ConfigError(f"routed experts: cannot use {self.top} of {self.n_experts} experts of width {self.ff}")
+        self.limit = float(params.get("limit", 0.0))
+        self.alpha = float(params.get("alpha", 1.0))
+        self.router_bias = bool(params.get("router_bias", True))
+        shared = params.get("shared")
+        self.shared_ff = int(shared["intermediate_size"]) if shared else 0
+        self.shared_limit = float(shared.get("limit", self.limit)) if shared else 0.0
+        self.names = dict(self.NAMES, **(params.get("tensors") or {}))
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
+
+    def _expert(self, e, m):
+        return self.names["expert"].format(e=e, m=m)
+
+    def weight_specs(self):
+        h = self.hidden_size
+        specs = {}
+        for e in range(self.n_experts):
+            specs[self._expert(e, "gate")] = WeightSpec((self.ff, h))
+            specs[self._expert(e, "up")] = WeightSpec((self.ff, h))
+            specs[self._expert(e, "down")] = WeightSpec((h, self.ff))
+        specs[self.names["router"]] = WeightSpec((self.n_experts, h), init=("normal", 0.1))
+        if self.router_bias:
+            specs[self.names["router_bias"]] = WeightSpec((self.n_experts,), "precise", ("normal", 0.1))
+        if self.shared_ff:
+            for m, shape in (("gate", (self.shared_ff, h)), ("up", (self.shared_ff, h)), ("down", (h, self.shared_ff))):
+                specs[self.names["shared"].format(m=m)] = WeightSpec(shape)
+        return specs
+
+    def bind(self, tensors):
+        E = range(self.n_experts)
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], dim=0)
+                                      for e in E]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in E]).contiguous()
+        self.w_router = tensors[self.names["router"]].contiguous()
+        self.b_router = tensors[self.names["router_bias"]].contiguous() if self.router_bias else None
+        if self.shared_ff:
+            name = self.names["shared"]
+            self.ws_gate_up = torch.cat([tensors[name.format(m="gate")], tensors[name.format(m="up")]], dim=0).contiguous()
+            self.ws_down = tensors[name.format(m="down")].contiguous()
+
+    def weight_bytes(self):
+        """Bytes a decode step of one token reads: the router, the chosen experts and the shared one."""
+        size = self.w_down.element_size()
+        chosen = 3 * self.ff * self.hidden_size * self.top
+        shared = 3 * self.shared_ff * self.hidden_size
+        return (self.w_router.numel() + chosen + shared) * size
+
+    def forward(self, x):
+        ids, weights = ops.route_topk(x, self.w_router, self.b_router, self.top)
+        h = ops.expert_gate_up(x, ids, self.w_gate_up, self.activation, self.limit, self.alpha)
+        shared = None
+        if self.shared_ff:
+            s = ops.gated_activation(ops.linear(x, self.ws_gate_up, resident=True), self.activation, self.shared_limit,
+                                     self.alpha)
+            shared = ops.linear(s, self.ws_down, out_dtype=torch.float32, resident=True)
+        return ops.expert_down(h, ids, weights, self.w_down, addend=shared)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

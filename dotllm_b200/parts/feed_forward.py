@@ -15,34 +15,44 @@ from .base import FeedForward, WeightSpec, register_feed_forward
 
 
 class GatedFeedForward(FeedForward):
-    """params: ``intermediate_size``, ``activation`` ("silu")."""
+    """params: ``intermediate_size``; ``activation``: "silu" (the fused products gate with it), or one of
+    ``ops.GATINGS`` ("gelu_tanh", "clamped_sigmoid" with ``limit`` and ``alpha``), which gate in a kernel of
+    their own behind the gate/up product; optional ``tensors``: the local names of the gate, up and down
+    matrices (default the HuggingFace ones)."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.intermediate_size = int(params["intermediate_size"])
-        if params.get("activation", "silu") != "silu":
-            raise ConfigError(f"gated feed-forward: unsupported activation {params['activation']!r}")
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.GATINGS:
+            raise ConfigError(f"gated feed-forward: unsupported activation {self.activation!r}; known: {sorted(ops.GATINGS)}")
+        self.limit = float(params.get("limit", 0.0))
+        self.alpha = float(params.get("alpha", 1.0))
+        names = params.get("tensors") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        self.gate_name, self.up_name, self.down_name = (str(n) for n in names)
+        self.takes_scaled_rows = self.activation == "silu"      # x goes straight into the gate/up product
         self.w_gate_up = None
         self.w_down = None
 
     def weight_specs(self):
         i, h = self.intermediate_size, self.hidden_size
-        return {"gate_proj.weight": WeightSpec((i, h)),
-                "up_proj.weight": WeightSpec((i, h)),
-                "down_proj.weight": WeightSpec((h, i))}
+        return {self.gate_name: WeightSpec((i, h)),
+                self.up_name: WeightSpec((i, h)),
+                self.down_name: WeightSpec((h, i))}
 
     def bind(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_gate_up = torch.cat([tensors[self.gate_name], tensors[self.up_name]], dim=0).contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
 
     def weight_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    takes_scaled_rows = True                    # x goes straight into the gate/up product
-
     def forward(self, x):
-        return ops.linear(ops.gated_linear(x, self.w_gate_up, resident=True), self.w_down, out_dtype=BRANCH_DTYPE,
-                          resident=True, lazy=True)
+        if self.activation == "silu":
+            gated = ops.gated_linear(x, self.w_gate_up, resident=True)
+        else:
+            gated = ops.gated_activation(ops.linear(x, self.w_gate_up, resident=True), self.activation, self.limit, self.alpha)
+        return ops.linear(gated, self.w_down, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
 
 register_feed_forward("gated_mlp", GatedFeedForward)

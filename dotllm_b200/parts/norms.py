@@ -12,19 +12,29 @@ from .base import Norm, WeightSpec, register_norm
 
 
 class RmsNorm(Norm):
-    """params: ``eps``; optional ``gain_init`` for the random-weights mode."""
+    """params: ``eps``; optional ``gain_init`` for the random-weights mode; optional ``offset``: the stored
+    tensor is the gain minus this number (1.0: a gain kept around zero, y = rms(x) * (1 + w); the sum is
+    taken once, in float32, when the weights are bound); optional ``tensor``: the local name of the stored
+    tensor (default "weight"; "" when the prefix is the whole name)."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.eps = float(params["eps"])
+        self.offset = float(params.get("offset", 0.0))
+        self.tensor_name = str(params.get("tensor", "weight"))
         self.gain = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.hidden_size,), "precise",
-                                     tuple(self.params.get("gain_init", ("ones",))))}
+        default = ("ones",) if self.offset == 0.0 else ("normal", 0.1)
+        return {self.tensor_name: WeightSpec((self.hidden_size,), "precise",
+                                             tuple(self.params.get("gain_init", default)))}
 
     def bind(self, tensors):
-        self.gain = tensors["weight"]
+        stored = tensors[self.tensor_name]
+        self.gain = stored if self.offset == 0.0 else (stored + self.offset).contiguous()
+
+    def branch(self, data):
+        return ops.NormedBranch(data, self.gain, self.eps)
 
     def weight_bytes(self):
         return self.gain.numel() * self.gain.element_size()

@@ -37,8 +37,12 @@ def check_names_and_shapes(available, expected, optional=()):
     WeightsError naming every problem."""
     missing = sorted(n for n in expected if n not in available)
     unexpected = sorted(n for n in available if n not in expected and n not in optional)
+    def fits(spec, found):
+        want, free = tuple(spec.shape), tuple(getattr(spec, "free_dims", ()))
+        return len(want) == len(found) and all(a == b or i in free for i, (a, b) in enumerate(zip(want, found)))
+
     wrong = sorted((n, tuple(expected[n].shape), tuple(available[n]))
-                   for n in expected if n in available and tuple(available[n]) != tuple(expected[n].shape))
+                   for n in expected if n in available and not fits(expected[n], tuple(available[n])))
     if not (missing or unexpected or wrong):
         return
     lines = ["the checkpoint does not match the model:"]

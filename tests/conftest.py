@@ -28,7 +28,8 @@ def cpu_kernels(monkeypatch):
     import kernel_refs
     from dotllm_b200.kernels import ops
     for name in ("gather_rows", "add_rmsnorm", "rope_cache_write", "attention", "swiglu", "linear", "gated_linear",
-                 "sample", "repetition_penalty"):
+                 "sample", "repetition_penalty", "add_normed_branch", "add_rows", "embed_positions", "gated_activation",
+                 "gla_scan", "head_norm_gate", "route_topk", "expert_gate_up", "expert_down", "linear_per_head"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     # ops.rope_cache_attention composes the two patched functions above for anything but CUDA bfloat16
     return kernel_refs

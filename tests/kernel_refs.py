@@ -24,9 +24,106 @@ def gather_rows(table, ids, out=None, out_dtype=torch.float32):
 
 
 def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
+    if hasattr(delta, "gain") and hasattr(delta, "extra"):          # a branch with a norm of its own
+        return add_normed_branch(residual, delta, gain, eps, out_dtype)
+    if hasattr(delta, "tensor"):
+        delta = delta.tensor()
     if delta is not None:
         residual += delta.to(torch.float32)
     return plain_llama.rms_norm(residual, gain, eps).to(out_dtype)
+
+
+def _rms(x, eps):
+    x = x.to(torch.float32)
+    return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+
+
+def add_normed_branch(residual, branch, gain=None, eps=0.0, out_dtype=None):
+    data = branch.data.tensor() if hasattr(branch.data, "tensor") else branch.data
+    residual += _rms(data, branch.eps) * branch.gain
+    if branch.extra is not None:
+        residual += branch.extra
+    return None if gain is None else (_rms(residual, eps) * gain).to(out_dtype)
+
+
+def add_rows(residual, other):
+    residual += other
+    return residual
+
+
+def embed_positions(table, pos_table, ids, positions):
+    return table[ids.long()].to(torch.float32) + pos_table[positions.long()].to(torch.float32)
+
+
+def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
+    i = gate_up.shape[1] // 2
+    g, u = gate_up[:, :i].to(torch.float32), gate_up[:, i:].to(torch.float32)
+    if kind == "silu":
+        y = g * torch.sigmoid(g) * u
+    elif kind == "gelu_tanh":
+        y = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u
+    else:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        y = g * torch.sigmoid(alpha * g) * (u + 1.0)
+    return y.to(gate_up.dtype)
+
+
+def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau):
+    T = q.shape[0]
+    out = torch.zeros((T, n_heads * vdim), dtype=torch.float32, device=q.device)
+    alpha = torch.exp(torch.nn.functional.logsigmoid(z.to(torch.float32) + z_bias) / tau).view(T, n_heads, dim)
+    qf = q.to(torch.float32).view(T, n_heads, dim) * q_scale
+    kf, vf = k.to(torch.float32).view(T, n_heads, dim), v.to(torch.float32).view(T, n_heads, vdim)
+    for b in range(slots.numel()):
+        S = state[int(slots[b])]
+        for t in range(int(cu_new[b]), int(cu_new[b + 1])):
+            S.mul_(alpha[t][:, :, None]).add_(kf[t][:, :, None] * vf[t][:, None, :])
+            out[t] = torch.einsum("hdv,hd->hv", S, qf[t]).reshape(-1)
+    return out
+
+
+def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
+    T = o.shape[0]
+    y = _rms(o.view(T, n_heads, vdim), eps) * gain
+    gf = g.to(torch.float32).reshape(T, n_heads, vdim)
+    return (y * gf * torch.sigmoid(gf)).reshape(T, n_heads * vdim).to(out_dtype)
+
+
+def route_topk(x, w_router, bias, top):
+    z = x.to(torch.float32) @ w_router.to(torch.float32).T
+    if bias is not None:
+        z = z + bias
+    ids = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
+    vals = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
+    for j in range(top):                                   # ties go to the lower index
+        best = z.max(dim=-1).values
+        at = (z == best[:, None]).to(torch.int32).argmax(dim=-1)
+        ids[:, j], vals[:, j] = at, best
+        z = z.scatter(1, at[:, None], float("-inf"))
+    return ids, torch.softmax(vals, dim=-1)
+
+
+def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0):
+    T, top = ids.shape
+    rows = [gated_activation(x[t:t + 1].to(torch.float32) @ w_gate_up[int(ids[t, j])].to(torch.float32).T, kind, limit, alpha)[0]
+            for t in range(T) for j in range(top)]
+    return torch.stack(rows).to(x.dtype) if rows else torch.zeros((0, w_gate_up.shape[1] // 2), dtype=x.dtype)
+
+
+def expert_down(h, ids, weights, w_down, addend=None):
+    T, top = ids.shape
+    out = torch.zeros((T, w_down.shape[1]), dtype=torch.float32, device=h.device)
+    for t in range(T):
+        for j in range(top):
+            out[t] += weights[t, j] * (w_down[int(ids[t, j])].to(torch.float32) @ h[t * top + j].to(torch.float32))
+    return out if addend is None else out + addend
+
+
+def linear_per_head(x, w):
+    H, b, a = w.shape
+    T = x.shape[0]
+    y = torch.einsum("tha,hba->thb", x.to(torch.float32).reshape(T, H, a), w.to(torch.float32))
+    return y.reshape(T, H * b).to(x.dtype)
 
 
 def _rotate(x, cos, sin, positions, n_heads, head_dim, rotary_dim):
