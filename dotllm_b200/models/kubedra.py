@@ -69,7 +69,7 @@ def build_kubedra_spec(cfg: KubedraConfig) -> ModelSpec:
         max_positions=cfg.max_positions,
         embedding=PartSpec("token_position_embedding",
                            {"vocab_size": cfg.vocab, "max_positions": cfg.max_positions,
-                            "token_tensor": "embed", "position_tensor": "pos"}, ""),
+                            "token_tensor": "embed", "position_tensor": "pos", "init_std": 0.5}, ""),
         layers=tuple(layers),
         schedule=tuple(ScheduleEntry(i, None, again) for i, again in cfg.layer_runs()),
         final_norm=_norm(cfg, "final.norm"),

@@ -37,7 +37,7 @@ class TokenEmbedding(Part):
 class TokenPositionEmbedding(Part):
     """Token embedding plus a learned vector per absolute position, neither scaled: h[t] = E[token] + P[pos].
     params: ``vocab_size``, ``max_positions``; optional ``token_tensor`` / ``position_tensor`` (local names,
-    default "weight" and "positions.weight")."""
+    default "weight" and "positions.weight") and ``init_std`` (of both tables in the random-weights mode)."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
@@ -48,8 +48,9 @@ class TokenPositionEmbedding(Part):
         self.table = self.positions = None
 
     def weight_specs(self):
-        return {self.token_name: WeightSpec((self.vocab_size, self.hidden_size)),
-                self.position_name: WeightSpec((self.max_positions, self.hidden_size))}
+        init = ("normal", float(self.params.get("init_std", 0.02)))
+        return {self.token_name: WeightSpec((self.vocab_size, self.hidden_size), init=init),
+                self.position_name: WeightSpec((self.max_positions, self.hidden_size), init=init)}
 
     def bind(self, tensors):
         self.table = tensors[self.token_name].contiguous()

@@ -1,0 +1,365 @@
+"""Kubedra on the GPU against the plain implementation: each mechanism's kernel alone, whole prompts, portions,
+token-by-token decoding, unequal batches, slots and pages that are used again, windows' edges, long decoding,
+generation through the entry point, the replay program."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kubedra as pk
+import tiny_kubedra as tk
+from dotllm_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = [torch.float32, torch.bfloat16]
+# A row's rms error over the row's rms.  float32: summation order only, every row is held to the bound.
+# bfloat16: both sides read the same bfloat16 weights; the engine rounds activations to bfloat16 between parts, through
+# up to seven layer runs (seen: median 8e-3, nine rows in ten below 1.3e-2).  A router whose two best logits nearly tie
+# may choose the other expert in bfloat16, which changes that token's row and no other (seen: up to 0.11 in two or three
+# rows of 150); so nine rows in ten are held to HALF the bound, all but 3 % to the bound, and none may exceed LOOSE.
+REL = {torch.float32: 3e-5, torch.bfloat16: 4e-2}
+LOOSE = 0.3
+
+
+def row_errors(got, want):
+    g, w = got.double().cpu().reshape(-1, got.shape[-1]), want.double().cpu().reshape(-1, want.shape[-1])
+    return (g - w).pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-30)
+
+
+def rel_err(got, want):
+    return float(row_errors(got, want).max())
+
+
+def assert_rows(got, want, dtype, what=""):
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    err = row_errors(got, want)
+    if dtype == torch.float32:
+        assert float(err.max()) <= REL[dtype], f"{what}: a row's rms error is {float(err.max()):.3e} of its rms > {REL[dtype]:.1e}"
+        return
+    over = int((err > REL[dtype]).sum())
+    assert float(err.max()) <= LOOSE and over <= max(1, int(0.03 * err.numel())), \
+        f"{what}: {over} of {err.numel()} rows beyond {REL[dtype]:.1e}, the worst {float(err.max()):.3e}"
+    if err.numel() >= 10:
+        assert float(err.quantile(0.9)) <= REL[dtype] / 2, f"{what}: nine rows in ten should be within {REL[dtype] / 2:.1e}"
+
+
+@pytest.fixture(scope="module")
+def tmp(tmp_path_factory):
+    return tmp_path_factory.mktemp("kubedra")
+
+
+_loaded = {}
+
+
+def load_pair(tmp, which, dtype, seed=0):
+    from dotllm_b200 import Model
+    key = (which, dtype, seed)
+    if key not in _loaded:
+        folder = tk.make_folder(tmp, which, seed=seed, dtype=dtype)
+        cfg, weights = tk.read_folder(folder)
+        _loaded[key] = (Model.load(folder, dtype=dtype), cfg, weights, folder)
+    return _loaded[key]
+
+
+def g64(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,dim,vdim", [(2, 24, 16), (1, 1, 1), (3, 130, 7), (2, 8, 70), (1, 256, 33)])
+def test_scan_kernel_alone(H, dim, vdim, dtype):
+    """The recurrence over three sequences of unequal lengths in one launch, from states that are not zero, then
+    continued token by token from what the first launch left; slots in no particular order."""
+    tau = 5.0
+    lens = [19, 1, 40]
+    T = sum(lens)
+    q, k, z = (g64(T, H * dim, seed=s).to(dtype) for s in (1, 2, 3))
+    v = g64(T, H * vdim, seed=4).to(dtype)
+    z = z.float() * 2
+    bias = g64(H * dim, seed=5).float()
+    state0 = g64(6, H, dim, vdim, seed=6).float()
+    slots = [4, 0, 3]
+    proj = torch.cat([q, k, v], dim=1).to(DEV)                      # column views of one matrix, as the mixer has them
+    qd, kd, vd = proj[:, :H * dim], proj[:, H * dim:2 * H * dim], proj[:, 2 * H * dim:]
+    cu = torch.tensor([0, 19, 20, 60], dtype=torch.int32, device=DEV)
+    state = state0.clone().to(DEV)
+    out = ops.gla_scan(qd, kd, vd, z.to(DEV), bias.to(DEV), cu, torch.tensor(slots, dtype=torch.int32, device=DEV), state,
+                       H, dim, vdim, dim ** -0.5, tau)
+    alpha = torch.sigmoid(z.double() + bias.double()).pow(1 / tau).view(T, H, dim)
+    at = 0
+    for n, slot in zip(lens, slots):
+        sl = slice(at, at + n)
+        want, s_want = pk.gla_recurrence(q[sl].double().view(n, H, dim) * dim ** -0.5, k[sl].double().view(n, H, dim),
+                                         v[sl].double().view(n, H, vdim), alpha[sl], state0[slot].double())
+        assert torch.allclose(out[sl].cpu().double().view(n, H, vdim), want, rtol=1e-4, atol=1e-4)
+        assert torch.allclose(state[slot].cpu().double(), s_want, rtol=1e-4, atol=1e-4)
+        at += n
+    assert torch.equal(state[[1, 2, 5]].cpu(), state0[[1, 2, 5]])       # slots of other sequences are not touched
+    # the first sequence again, its last 6 tokens one launch each: the same bits as in one launch
+    state = state0.clone().to(DEV)
+    one = torch.tensor([4], dtype=torch.int32, device=DEV)
+    parts = [ops.gla_scan(qd[:13], kd[:13], vd[:13], z[:13].to(DEV), bias.to(DEV),
+                          torch.tensor([0, 13], dtype=torch.int32, device=DEV), one, state, H, dim, vdim, dim ** -0.5, tau)]
+    for t in range(13, 19):
+        parts.append(ops.gla_scan(qd[t:t + 1], kd[t:t + 1], vd[t:t + 1], z[t:t + 1].to(DEV), bias.to(DEV),
+                                  torch.tensor([0, 1], dtype=torch.int32, device=DEV), one, state, H, dim, vdim, dim ** -0.5, tau))
+    assert torch.equal(torch.cat(parts), out[:19])
+
+
+def test_decay_keeps_its_digits_where_the_sigmoid_is_tiny():
+    """alpha = sigmoid(z)^(1/tau) for z far below zero: through the logarithm it is exp(z / tau), not 0^(1/tau)."""
+    H, dim, vdim, tau = 1, 4, 2, 16.0
+    z = torch.tensor([[-120.0, -40.0, 0.0, 30.0]], device=DEV).repeat(2, 1)
+    ones = torch.ones(2, 4 + 4 + 2, device=DEV)
+    state = torch.zeros(1, 1, 4, 2, device=DEV)
+    ops.gla_scan(ones[:, :4], ones[:, 4:8], ones[:, 8:], z, torch.zeros(4, device=DEV),
+                 torch.tensor([0, 2], dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV), state,
+                 H, dim, vdim, 1.0, tau)
+    alpha = torch.sigmoid(z[0].double().cpu()).log().div(tau).exp()
+    assert torch.allclose(state[0, 0, :, 0].cpu().double(), 1 + alpha, rtol=1e-5)
+    assert 1e-4 < float(state[0, 0, 0, 0]) - 1 < 1e-3                # exp(-120 / 16), which 32-bit sigmoid(-120) = 0 would lose
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_norm_router_experts_and_branch_norm_kernels(dtype):
+    tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    # per-head norm and gate
+    T, H, vdim, eps = 9, 3, 20, 1e-5
+    o, gate, gain = g64(T, H * vdim, seed=1).float(), g64(T, H * vdim, seed=2).to(dtype), (1 + g64(vdim, seed=3, scale=0.1)).float()
+    got = ops.head_norm_gate(o.to(DEV), gate.to(DEV), gain.to(DEV), H, vdim, eps, dtype)
+    want = pk.plain_norm(o.double().view(T, H, vdim), gain.double(), eps).reshape(T, -1) * torch.nn.functional.silu(gate.double())
+    assert torch.allclose(got.cpu().double(), want, **tol)
+    # router: the largest logits, ties to the lower index, softmax over the chosen alone
+    T, K, E, top = 11, 40, 7, 3
+    x, wr, b = g64(T, K, seed=4).to(dtype), g64(E, K, seed=5, scale=0.3).to(dtype), g64(E, seed=6).float()
+    wr[3] = wr[1]
+    b[3] = b[1]                                                     # two experts that always tie
+    ids, wts = ops.route_topk(x.to(DEV), wr.to(DEV), b.to(DEV), top)
+    w = {"r.router": wr.double(), "r.router.b": b.double()}
+    zfull = x.double() @ wr.double().T + b.double()
+    for t in range(T):
+        got_ids = ids[t].tolist()
+        assert sorted(zfull[t, got_ids].tolist(), reverse=True) == torch.topk(zfull[t], top).values.tolist()
+        assert not (3 in got_ids and 1 not in got_ids)
+        assert torch.allclose(wts[t].cpu().double(), torch.softmax(zfull[t, got_ids], -1), rtol=1e-4, atol=1e-5)
+    # experts: every token's own choice, weights and a shared addend
+    ff, limit = 24, 1.25
+    weights = {"m.router": wr.double(), "m.router.b": b.double()}
+    for e in range(E):
+        weights[f"m.e{e}.gate"], weights[f"m.e{e}.up"] = g64(ff, K, seed=10 + e, scale=0.4).to(dtype), g64(ff, K, seed=30 + e, scale=0.4).to(dtype)
+        weights[f"m.e{e}.down"] = g64(K, ff, seed=50 + e, scale=0.3).to(dtype)
+    w_gu = torch.stack([torch.cat([weights[f"m.e{e}.gate"], weights[f"m.e{e}.up"]]) for e in range(E)]).to(DEV)
+    w_d = torch.stack([weights[f"m.e{e}.down"] for e in range(E)]).to(DEV)
+    h = ops.expert_gate_up(x.to(DEV), ids, w_gu, "clamped_sigmoid", limit, 1.702)
+    addend = g64(T, K, seed=7).float()
+    got = ops.expert_down(h, ids, wts, w_d, addend.to(DEV))
+    want = torch.zeros(T, K, dtype=torch.float64)
+    for t in range(T):
+        for e, gw in zip(ids[t].tolist(), wts[t].tolist()):
+            want[t] += gw * pk.clamped_expert(x[t:t + 1].double(), {k: v.double() for k, v in weights.items()}, f"m.e{e}.", limit)[0]
+    assert torch.allclose(got.cpu().double(), want + addend.double(), **tol)
+    assert float(h.float().abs().max()) <= limit * (limit + 1) + 1e-2        # both clamps bite at these scales
+    # gatings
+    gu = g64(5, 2 * 17, seed=8, scale=2.0).to(dtype)
+    want = pk.gelu_tanh(gu[:, :17].double()) * gu[:, 17:].double()
+    assert torch.allclose(ops.gated_activation(gu.to(DEV), "gelu_tanh").cpu().double(), want, **tol)
+    # a branch that is normalised, added (with an extra addend) and the sum normalised, in one kernel
+    for width in (40, 1100):
+        res, d, extra = g64(6, width, seed=9).float(), g64(6, width, seed=10, scale=4).to(dtype), g64(6, width, seed=11).float()
+        dg, gn = g64(width, seed=12, scale=0.1).float(), g64(width, seed=13, scale=0.1).float()
+        stream = res.clone().to(DEV)
+        out = ops.add_rmsnorm(stream, ops.NormedBranch(d.to(DEV), (1 + dg).to(DEV), 1e-6, extra.to(DEV)), (1 + gn).to(DEV), 1e-6, dtype)
+        want_stream = res.double() + pk.offset_norm(d.double(), dg.double(), 1e-6) + extra.double()
+        assert torch.allclose(stream.cpu().double(), want_stream, rtol=1e-5, atol=1e-5)
+        assert torch.allclose(out.cpu().double(), pk.offset_norm(want_stream, gn.double(), 1e-6), **tol)
+    # embedding with positions
+    table, pos = g64(30, 24, seed=14).to(dtype), g64(50, 24, seed=15).to(dtype)
+    ids_, at = torch.tensor([3, 29, 0], dtype=torch.int32), torch.tensor([49, 0, 7], dtype=torch.int32)
+    got = ops.embed_positions(table.to(DEV), pos.to(DEV), ids_.to(DEV), at.to(DEV))
+    assert torch.equal(got.cpu(), table[ids_.long()].float() + pos[at.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [3, 50])
+def test_products_per_head(T, dtype):
+    x, w = g64(T, 4 * 24, seed=1).to(dtype), g64(4, 10, 24, seed=2, scale=0.2).to(dtype)
+    want = torch.einsum("tha,hba->thb", x.double().view(T, 4, 24), w.double()).reshape(T, 40)
+    got = ops.linear_per_head(x.to(DEV), w.to(DEV))
+    assert torch.allclose(got.cpu().double(), want, **(dict(atol=1e-5) if dtype == torch.float32 else dict(atol=3e-2)))
+
+
+# ------------------------------------------------------------------ the model
+def run_cuts(model, tokens, cuts, want_all=True):
+    """Logits at every position of one sequence fed in portions of the given sizes (the rest one by one)."""
+    from dotllm_b200.engine import StepEntry
+    cache = model.new_cache(64 * ((len(tokens) + 63) // 64 + 1))
+    cache.fill_free_pages(float("nan"))
+    seq = cache.open_sequence()
+    outs, at = [], 0
+    sizes = list(cuts)
+    while at < len(tokens):
+        n = min(sizes.pop(0) if sizes else 1, len(tokens) - at)
+        outs.append(model.step(cache, [StepEntry(seq, tokens[at:at + n], list(range(n)))]).clone())
+        at += n
+    cache.close_sequence(seq)
+    cache.check()
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["P", "Q", "R"])
+def test_whole_portions_and_decoding(tmp, which, dtype):
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    tokens = tk.random_tokens(150, cfg["vocab"], 7)
+    ref = pk.forward(cfg, w, tokens)
+    whole = run_cuts(model, tokens, [150])
+    assert_rows(whole, ref, dtype, "whole prompt")
+    for cuts in ([64, 2, 2, 62, 20], [1, 5, 17, 33, 64, 30], [129, 2], [140]):          # [140]: the last ten one by one
+        got = run_cuts(model, tokens, cuts)
+        assert_rows(got, ref, dtype, f"portions {cuts}")
+        if dtype == torch.float32:
+            assert rel_err(got, whole) < 1e-5, cuts
+    assert_rows(run_cuts(model, tokens[:40], []), ref[:40], dtype, "token by token from the first")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["P", "Q"])
+def test_unequal_batches_slots_and_pages_used_again(tmp, which, dtype):
+    from dotllm_b200.engine import StepEntry
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    lens = [1, 70, 23, 131]
+    prompts = [tk.random_tokens(n + 12, cfg["vocab"], 20 + n) for n in lens]
+    refs = [pk.forward(cfg, w, p) for p in prompts]
+    cache = model.new_cache(64 * 8)
+    for round_ in range(2):                                          # the second time every slot and page has been used before
+        cache.fill_free_pages(float("nan"))
+        seqs = [cache.open_sequence() for _ in prompts]
+        order = list(range(len(prompts))) if round_ == 0 else [2, 0, 3, 1]
+        out = model.step(cache, [StepEntry(seqs[i], prompts[i][:lens[i]], [0, lens[i] - 1]) for i in order])
+        want = torch.cat([refs[i][[0, lens[i] - 1]] for i in order])
+        assert_rows(out, want, dtype, "a batch of unequal prompts")
+        live = list(order)
+        for t in range(12):
+            if t == 5:
+                gone = live.pop(1)                                   # a request ends early; its slot and pages go back ...
+                cache.close_sequence(seqs[gone])
+                cache.fill_free_pages(float("nan"))
+            out = model.step(cache, [StepEntry(seqs[i], [prompts[i][lens[i] + t]]) for i in live])
+            assert_rows(out, torch.stack([refs[i][lens[i] + t] for i in live]), dtype, f"decoding together, step {t}")
+        for i in live:
+            cache.close_sequence(seqs[i])
+        cache.check()
+    assert not cache.live
+
+
+def test_window_edges_decide_whole_rows(tmp):
+    """One latent-attention layer whose scores are scaled until the softmax all but picks a single key.  Where that key
+    is the oldest one the window still holds, a window that is one token short gives another row of logits, and where
+    the best key lies just outside, a window one token long does.  The plain implementation with the window moved by
+    one must therefore differ visibly, and the engine must agree with the right one: in a prompt, across a portion's
+    start, and when decoding moves the window over decoded tokens and page borders."""
+    import copy
+    dtype = torch.float32
+    model, cfg, w, _ = load_pair(tmp, "latent_only", dtype)
+    window = cfg["layers"][0]["mixer"]["mask"]["size"]
+    tokens = tk.random_tokens(260, cfg["vocab"], 3)
+    ref = pk.forward(cfg, w, tokens)
+    for moved in (-1, 1):
+        other = copy.deepcopy(cfg)
+        other["layers"][0]["mixer"]["mask"]["size"] = window + moved
+        diff = (pk.forward(other, w, tokens) - ref).pow(2).mean(-1).sqrt() / ref.pow(2).mean(-1).sqrt()
+        assert int((diff > 1e-2).sum()) >= 3, "the test's weights do not show a moved window"
+        assert float(diff[:window - 1].max()) == 0.0                 # before the window is full nothing can differ
+    for cuts in ([260], [window - 1, 1, 1, 100], [window + 30], [200]):
+        got = run_cuts(model, tokens, cuts)
+        assert rel_err(got, ref) < 1e-4, cuts
+    bf = load_pair(tmp, "latent_only", torch.bfloat16)
+    got = run_cuts(bf[0], tokens, [100])
+    ref16 = pk.forward(bf[1], bf[2], tokens)
+    row_err = (got.double().cpu() - ref16).pow(2).mean(-1).sqrt() / ref16.pow(2).mean(-1).sqrt()
+    assert float(row_err.median()) < 2e-2 and int((row_err > 0.2).sum()) <= 2      # a near-tie may flip in bfloat16, a window may not
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_through_a_slow_decay(tmp, dtype):
+    """One recurrent layer with tau = 64: a token hundreds of steps back still weighs in the state.  Decoding 600 tokens
+    one by one after a short prompt must track the plain implementation, and the plain implementation with the first
+    tokens' contribution removed must not."""
+    model, cfg, w, _ = load_pair(tmp, "gla_only", dtype)
+    tokens = tk.random_tokens(640, cfg["vocab"], 5)
+    ref = pk.forward(cfg, w, tokens)
+    forgot = pk.forward(cfg, w, tokens[40:])                         # the same tail without the first 40 tokens (positions differ too)
+    assert rel_err(forgot[-50:], ref[-50:]) > 1e-2
+    got = run_cuts(model, tokens, [40])
+    assert_rows(got, ref, dtype, "600 decoded tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["P", "Q"])
+def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
+    from dotllm_b200 import InferenceOptions
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    prompts = [tk.random_tokens(n, cfg["vocab"], 60 + n) for n in (1, 9, 40, 70)]
+    n_new = 24
+    outs = model.generate(prompts, InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason.value == "length" and o.generated_token_count == n_new
+        ref = pk.forward(cfg, w, p + o.generated_token_ids)
+        spread = float(ref.std())
+        for i, tok in enumerate(o.generated_token_ids):              # teacher-forced: the plain arg-max, or within rounding of it
+            row = ref[len(p) - 1 + i]
+            assert int(row.argmax()) == tok or float(row.max() - row[tok]) <= (1e-4 if dtype == torch.float32 else 0.1) * spread, \
+                (i, tok, int(row.argmax()))
+    again = model.generate(prompts, InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))      # through captured steps now
+    alone = model.generate(prompts[2], InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    if dtype == torch.float32:
+        assert [o.generated_token_ids for o in again] == [o.generated_token_ids for o in outs]
+        assert alone.generated_token_ids == outs[2].generated_token_ids
+
+
+def test_decode_steps_replayed_from_graphs_keep_their_state(tmp):
+    """Steps captured as graphs (exact batch size and the shared widths with idle rows) give the eager steps' logits,
+    and the trial run before a capture does not advance the recurrent state."""
+    from dotllm_b200.engine import StepEntry
+    dtype = torch.float32
+    model, cfg, w, _ = load_pair(tmp, "P", dtype)
+    prompts = [tk.random_tokens(n + 10, cfg["vocab"], 80 + n) for n in (5, 66, 30)]
+    refs = [pk.forward(cfg, w, p) for p in prompts]
+    for graphs in (True, "lazy"):
+        cache = model.new_cache(64 * 6)
+        seqs = [cache.open_sequence() for _ in prompts]
+        model.step(cache, [StepEntry(s, p[:-10], []) for s, p in zip(seqs, prompts)])
+        for t in range(10):
+            out = model.step(cache, [StepEntry(s, [p[len(p) - 10 + t]]) for s, p in zip(seqs, prompts)], graphs=graphs)
+            assert_rows(out, torch.stack([r[len(r) - 10 + t] for r in refs]), dtype, f"graphs={graphs} step {t}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program_on_a_kubedra_folder(tmp_path, dtype):
+    tdtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    folder = tk.make_folder(tmp_path, "Q", seed=2, dtype=tdtype)
+    cfg, w = tk.read_folder(folder)
+    a, b = tk.random_tokens(90, cfg["vocab"], 1), tk.random_tokens(30, cfg["vocab"], 2)
+    ra, rb = pk.forward(cfg, w, a), pk.forward(cfg, w, b)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:80], "want": [0, 79]}, {"id": "b", "tokens": b[:20], "want": []}], "end": []}]
+    for t in range(10):
+        steps.append({"step": t + 1, "entries": [{"id": "a", "tokens": [a[80 + t]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[20 + t]], "want": [0] if t % 2 else []}],
+                      "end": ["a", "b"] if t == 9 else []})
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out_dir),
+                           "--max-tokens", "256"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [x for s in steps for x in ("done", str(s["step"]))]
+    read = lambda n: torch.from_numpy(np.fromfile(out_dir / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+    assert_rows(read(0), ra[[0, 79]], tdtype, "prompt step")
+    for t in range(10):
+        want = [ra[80 + t]] + ([rb[20 + t]] if t % 2 else [])
+        assert_rows(read(t + 1), torch.stack(want), tdtype, f"decode step {t}")
