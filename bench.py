@@ -5,6 +5,7 @@
     python bench.py --shape 1b --workload unequal     # 64 prompts of 16..2048 tokens in one step, then 256 decode steps
     python bench.py --workload staggered              # Model.generate while 64 requests end one by one (also --shape 1b)
     python bench.py --workload short-prompts          # time to the first token of single short prompts, eager and captured
+    python bench.py --workload kubedra [--shape 1b]   # the Kubedra design beside a Llama of equal width and depth, and its kernels
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -126,10 +127,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts"],
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra"],
                     help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
                          "staggered: Model.generate on 64 prompts whose requests end five steps apart; "
-                         "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens")
+                         "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens; "
+                         "kubedra: prefill and decode of the Kubedra design at layer sizes of a real model beside a Llama of "
+                         "equal width and depth, and each of its kernels against its roofline")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -159,6 +162,8 @@ def main():
     from dotllm_b200.config import config_from_dict
     from dotllm_b200.kernels import library, ops
 
+    if args.workload == "kubedra":
+        return kubedra_workload(args)
     pk = peaks()
     shape_name, shape = SHAPES[args.shape]
     cfg_dict = dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"])
@@ -407,6 +412,178 @@ def main():
     if generate:
         line["generate"] = generate
     print(json.dumps(line))
+    return 0
+
+
+KUBEDRA_SIZES = {
+    # width, heads and feed-forward of the Llama shape of the same name; four layers, one of each pairing of mixer and feed-forward
+    "1b": dict(width=2048, heads=16, key=64, value=128, q_rank=768, kv_rank=128, att_dim=128, window=1024, ff=8192,
+               experts=16, top=2, expert_ff=2048, shared_ff=2048, llama=dict(heads=16, kv_heads=4, head_dim=128, ff=8192)),
+    "8b": dict(width=4096, heads=32, key=64, value=128, q_rank=1536, kv_rank=128, att_dim=128, window=1024, ff=14336,
+               experts=32, top=4, expert_ff=2048, shared_ff=2048, llama=dict(heads=32, kv_heads=8, head_dim=128, ff=14336)),
+}
+
+
+def kubedra_workload(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
+    Kubedra model at a real model's layer sizes, beside a four-layer Llama of the same width, head count and feed-forward
+    width; then every kernel of the new design alone against its roofline (bytes it must move over the measured copy
+    bandwidth, or arithmetic over the measured bf16 rate), beside the like kernel of the Llama path.  Random weights,
+    synthetic tokens, bfloat16, CUDA events, an L2 flush between the timed launches of a kernel."""
+    import numpy as np
+    import torch
+    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.kernels import ops
+    pk = peaks()
+    hbm, tflops = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    sizes = ["1b", "8b"] if args.shape not in ("1b",) else ["1b"]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    gen = torch.Generator().manual_seed(1)
+    reps, T, ctx = max(3, args.repeats), args.prefill_tokens, 2048
+    sampler = ClockSampler()
+
+    def timed(fn, n=None, flushed=True):
+        n = n or reps
+        out = []
+        for it in range(3 + n):
+            if flushed:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                out.append(a.elapsed_time(b))
+        return statistics.median(out)
+
+    def model_points(model, vocab):
+        res = {}
+        prompt = np.asarray(torch.randint(0, vocab, (T,), generator=gen))
+        cache = model.new_cache(max_tokens=64 * (ctx + 192), max_sequences=64)
+
+        def prefill():
+            s = cache.open_sequence()
+            model.step(cache, [StepEntry(s, prompt)])
+            cache.close_sequence(s)
+        ms = timed(prefill, flushed=False)
+        res["prefill_tok_s"] = round(T * 1000.0 / ms, 1)
+        res["prefill_ms"] = round(ms, 3)
+        for batch in (8, 64):
+            seqs = [cache.open_sequence() for _ in range(batch)]
+            for lo in range(0, batch, 8):                       # fill the contexts through the model, eight prompts a step
+                model.step(cache, [StepEntry(s, np.asarray(torch.randint(0, vocab, (ctx,), generator=gen)), []) for s in seqs[lo:lo + 8]])
+            ids = [[int(t)] for t in torch.randint(0, vocab, (batch,), generator=gen)]
+            step = lambda: model.step(cache, [StepEntry(s, t) for s, t in zip(seqs, ids)], graphs=True)
+            for _ in range(max(3, args.warmup)):
+                step()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                step()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / args.steps
+            res[f"decode_b{batch}_tok_s"] = round(batch * 1000.0 / ms, 1)
+            res[f"decode_b{batch}_ms"] = round(ms, 3)
+            for s in seqs:
+                cache.close_sequence(s)
+        return res
+
+    def kernel_table(z):
+        """Each kernel alone: (microseconds, fraction of its roofline) at prefill (T rows) and decode (64 rows) sizes."""
+        W, H, dk, dv, r, E, top, ff = z["width"], z["heads"], z["key"], z["value"], z["kv_rank"], z["experts"], z["top"], z["expert_ff"]
+        bf = torch.bfloat16
+        rows = {}
+
+        def row(name, fn, bytes_=0, flops=0):
+            us = timed(fn) * 1000.0
+            need = max(bytes_ / hbm, flops / tflops) * 1e6
+            rows[name] = {"us": round(us, 1), "roofline_us": round(need, 2), "frac": round(need / us, 4)}
+        for label, n, n_seqs in (("prefill", T, 1), ("decode", 64, 64)):
+            x = torch.randn(n, W, device=dev).to(bf)
+            stream, delta = torch.randn(n, W, device=dev), torch.randn(n, W, device=dev)
+            gain = torch.ones(W, device=dev)
+            # the norm between sublayers: new (branch normalised, added, sum normalised) and old (added, normalised)
+            row(f"branch_norm_add {label}", lambda: ops.add_rmsnorm(stream, ops.NormedBranch(delta, gain, 1e-5), gain, 1e-5, bf),
+                bytes_=n * W * (4 + 4 + 4 + 2))
+            row(f"llama add_rmsnorm {label}", lambda: ops.add_rmsnorm(stream, delta, gain, 1e-5, bf), bytes_=n * W * (4 + 4 + 4 + 2))
+            # gated linear attention: the scan and the per-head norm with its gate
+            kw, vw = H * dk, H * dv
+            proj = torch.randn(n, 2 * kw + 2 * vw, device=dev).to(bf)
+            zz, zb = torch.randn(n, kw, device=dev), torch.zeros(kw, device=dev)
+            state = torch.zeros(n_seqs + 1, H, dk, dv, device=dev)
+            cu = torch.arange(0, n + 1, n // n_seqs, dtype=torch.int32, device=dev)
+            slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+            scan = lambda: ops.gla_scan(proj[:, :kw], proj[:, kw:2 * kw], proj[:, 2 * kw:2 * kw + vw], zz, zb, cu, slots, state,
+                                        H, dk, dv, dk ** -0.5, 16.0)
+            io = n * (2 * kw * 2 + vw * 2 + kw * 4 + vw * 4) + 2 * n_seqs * H * dk * dv * 4
+            row(f"gla_scan {label}", scan, bytes_=io, flops=4 * n * H * dk * dv)
+            o = scan()
+            row(f"head_norm_gate {label}", lambda: ops.head_norm_gate(o, proj[:, 2 * kw + vw:], torch.ones(dv, device=dev), H, dv, 1e-5, bf),
+                bytes_=n * vw * (4 + 2 + 2))
+            # experts
+            wr, wgu = torch.randn(E, W, device=dev).to(bf), (torch.randn(E, 2 * ff, W, device=dev) * 0.02).to(bf)
+            wd = (torch.randn(E, W, ff, device=dev) * 0.02).to(bf)
+            ids, wts = ops.route_topk(x, wr, None, top)
+            used = min(E, n * top)
+            row(f"route_topk {label}", lambda: ops.route_topk(x, wr, None, top), bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
+            row(f"expert_gate_up {label}", lambda: ops.expert_gate_up(x, ids, wgu, "clamped_sigmoid", 7.0, 1.702),
+                bytes_=used * 2 * ff * W * 2 + n * W * 2 + n * top * ff * 2, flops=2 * n * top * 2 * ff * W)
+            h = ops.expert_gate_up(x, ids, wgu, "clamped_sigmoid", 7.0, 1.702)
+            row(f"expert_down {label}", lambda: ops.expert_down(h, ids, wts, wd), bytes_=used * ff * W * 2 + n * top * ff * 2 + n * W * 4,
+                flops=2 * n * top * ff * W)
+            if ops.experts_grouped_takes(x, ids, wgu, wd):
+                # the path a step of this many rows takes: sort, gather, two tcgen05 products, weighted sum
+                row(f"experts sorted on tensor cores {label}", lambda: ops.experts_grouped(x, ids, wts, wgu, wd, "clamped_sigmoid", 7.0, 1.702),
+                    bytes_=used * 3 * ff * W * 2 + n * W * (2 + 4) + n * top * (W * 2 + ff * 4 + W * 8), flops=2 * n * top * 3 * ff * W)
+            # the like kernel of the Llama path: the dense gated product of the same rows
+            wl = (torch.randn(2 * z["ff"], W, device=dev) * 0.02).to(bf)
+            row(f"llama gated product {label}", lambda: ops.gated_linear(x, wl, resident=True),
+                bytes_=2 * z["ff"] * W * 2 + n * W * 2 + n * z["ff"] * 2, flops=2 * n * 2 * z["ff"] * W)
+            del wgu, wd, wl
+        return rows
+
+    out = {}
+    for name in sizes:
+        z = KUBEDRA_SIZES[name]
+        mix_g = {"heads": z["heads"], "dim": z["key"], "vdim": z["value"], "tau": 16.0, "decay_rank": 64}
+        mix_l = {"heads": z["heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+                 "mask": {"size": z["window"]}}
+        moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+               "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+        dense = {"kind": "dense", "ff": z["ff"]}
+        vocab = 32000
+        kcfg = {"architecture": "Kubedra", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "layers": [{"type": "gla", "mixer": mix_g, "mlp": dense}, {"type": "gla", "mixer": mix_g, "mlp": moe},
+                           {"type": "latent_attention", "mixer": mix_l, "mlp": moe},
+                           {"type": "latent_attention", "mixer": mix_l, "mlp": dense}]}
+        la = z["llama"]
+        lcfg = dict(LLAMA_31_8B, num_hidden_layers=4, hidden_size=z["width"], num_attention_heads=la["heads"],
+                    num_key_value_heads=la["kv_heads"], head_dim=la["head_dim"], intermediate_size=la["ff"], vocab_size=vocab,
+                    max_position_embeddings=8192, tie_word_embeddings=True)
+        point = {}
+        for label, cfg_dict in (("kubedra", kcfg), ("llama", lcfg)):
+            model = Model.random(config_from_dict(cfg_dict), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+            point[label] = model_points(model, vocab)
+            print(f"[bench] {name} {label}: {point[label]}", file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        point["kernels"] = kernel_table(z)
+        for k, v in point["kernels"].items():
+            print(f"[bench] {name} {k}: {v}", file=sys.stderr, flush=True)
+        out[name] = point
+    first = out[sizes[0]]
+    print(json.dumps({"metric": "kubedra_decode_tokens_per_second", "value": first["kubedra"]["decode_b8_tok_s"], "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
+                      "config": {"model": "Kubedra, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
+                                 "l2": "flushed between a kernel's timed launches"},
+                      "peaks": pk, "sizes": out}))
     return 0
 
 

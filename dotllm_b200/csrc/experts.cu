@@ -201,3 +201,108 @@ extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* we
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));
     return DL_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Many rows (a prompt, a large decode batch): the rows are sorted by expert so that a tensor-core
+// product can take an expert's rows as tiles (dl_gemm_tc_grouped_bf16).  Everything is decided on the
+// device: one block counts the rows of each expert, lays the experts' runs out one behind the other,
+// each padded to whole tiles of EX_TILE rows, gives every (token, choice) row its place in its
+// expert's run, and names each tile's expert.  Which place within a run a row gets depends on the
+// order in which threads arrive; no result depends on it (a row's products do not depend on the
+// other rows of its tile).
+#define EX_TILE 128
+#define EX_SORT_THREADS 1024
+
+__global__ void __launch_bounds__(EX_SORT_THREADS)
+expert_sort_kernel(const int32_t* __restrict__ ids, int rows, int E, int32_t* __restrict__ place, int32_t* __restrict__ tile_expert,
+                   int max_tiles) {
+    extern __shared__ int sort_smem[];               // [E] counts, then [E] cursors
+    int* counts = sort_smem;
+    int* cursor = sort_smem + E;
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < E; ++e) {
+            cursor[e] = tile * EX_TILE;
+            const int n = (counts[e] + EX_TILE - 1) / EX_TILE;
+            for (int b = 0; b < n && tile < max_tiles; ++b) tile_expert[tile++] = e;
+        }
+        for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        const int e = ids[i];
+        place[i] = (e >= 0 && e < E) ? atomicAdd(&cursor[e], 1) : -1;
+    }
+}
+
+// sorted[place[r], :] = x[r / top, :]   (16 bytes a thread)
+__global__ void __launch_bounds__(256)
+expert_gather_kernel(const uint4* __restrict__ x, int x_stride16, const int32_t* __restrict__ place, uint4* __restrict__ sorted,
+                     int top, int k16) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int r = blockIdx.x;
+    const int p = place[r];
+    if (p < 0) return;
+    const uint4* src = x + (size_t)(r / top) * x_stride16;
+    uint4* dst = sorted + (size_t)p * k16;
+    for (int c = threadIdx.x; c < k16; c += blockDim.x) dst[c] = src[c];
+}
+
+// out[t, n] = sum_j weights[t, j] * y[place[t * top + j], n]  (+ addend[t, n]), float32
+__global__ void __launch_bounds__(256)
+expert_combine_kernel(const float* __restrict__ y, int y_stride, const int32_t* __restrict__ place, const float* __restrict__ weights,
+                      const float* __restrict__ addend, int addend_stride, float* __restrict__ out, int top, int N) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int t = blockIdx.x;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int p = place[(size_t)t * top + j];
+            if (p >= 0) total += weights[(size_t)t * top + j] * y[(size_t)p * y_stride + n];
+        }
+        out[(size_t)t * N + n] = total + (addend != nullptr ? addend[(size_t)t * addend_stride + n] : 0.f);
+    }
+}
+
+// ids int32 [rows] (rows = tokens * top); place int32 [rows]; tile_expert int32 [max_tiles], max_tiles >= rows / 128 + E.
+extern "C" int dl_expert_sort(const int32_t* ids, int rows, int E, int32_t* place, int32_t* tile_expert, int max_tiles, void* stream) {
+    DL_REQUIRE(rows >= 0 && E > 0 && max_tiles >= (rows + EX_TILE - 1) / EX_TILE + E - 1, "expert_sort: %d tiles do not hold %d rows of %d experts",
+               max_tiles, rows, E);
+    DL_REQUIRE((size_t)2 * E * sizeof(int) <= 48 * 1024, "expert_sort: too many experts");
+    cudaError_t e = dl_launch_dependent(expert_sort_kernel, dim3(1), dim3(EX_SORT_THREADS), (size_t)2 * E * sizeof(int),
+                                        (cudaStream_t)stream, ids, rows, E, place, tile_expert, max_tiles);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_sort: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
+// x bfloat16 [tokens, K] (rows x_stride apart, 16-byte aligned, K a multiple of 8); sorted bfloat16 [padded rows, K].
+extern "C" int dl_expert_gather(const void* x, int x_stride, const int32_t* place, void* sorted, int rows, int top, int K, void* stream) {
+    DL_REQUIRE(rows >= 0 && top > 0 && K > 0 && K % 8 == 0 && x_stride % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)sorted % 16) == 0,
+               "expert_gather: rows of a multiple of 8 bfloat16 values, 16-byte aligned");
+    if (rows == 0) return DL_OK;
+    cudaError_t e = dl_launch_dependent(expert_gather_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x,
+                                        x_stride / 8, place, (uint4*)sorted, top, K / 8);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gather: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
+extern "C" int dl_expert_combine(const float* y, int y_stride, const int32_t* place, const float* weights, const float* addend,
+                                 int addend_stride, float* out, int tokens, int top, int N, void* stream) {
+    DL_REQUIRE(tokens >= 0 && top > 0 && N > 0 && y_stride >= N, "expert_combine: bad sizes");
+    if (tokens == 0) return DL_OK;
+    cudaError_t e = dl_launch_dependent(expert_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, y, y_stride, place,
+                                        weights, addend, addend_stride, out, top, N);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_combine: %s", cudaGetErrorString(e));
+    return DL_OK;
+}

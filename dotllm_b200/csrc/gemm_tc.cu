@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
+#include "gating.cuh"
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -81,7 +82,20 @@ __device__ __forceinline__ void gt_store32<float>(float* row_ptr, int col0, int 
     }
 }
 
-enum { GT_PLAIN = 0, GT_GATED = 1, GT_QKV = 2 };
+enum { GT_PLAIN = 0, GT_GATED = 1, GT_QKV = 2, GT_GROUPED_GATED = 3, GT_GROUPED = 4 };
+
+// Grouped products (a feed-forward of experts): the rows of x are sorted by expert, every expert's run of rows
+// padded to whole tiles of 128, and `tile_expert[tm]` names the expert of row tile tm (-1: a tile behind the
+// last run, which nobody computes).  W is the experts' matrices one below the other, `rows_per_expert` rows
+// each; a tile of the output multiplies its rows by the matrix of its expert.  Gated: an expert's matrix is
+// `up_offset` gate rows followed by as many up rows, and the gating is one of gating.cuh.
+struct GtGroups {
+    const int32_t* tile_expert;
+    int rows_per_expert;
+    int up_offset;
+    int gate_kind;
+    float limit, alpha;
+};
 
 // What the Q/K/V epilogue needs: the columns' split, the rotary tables, where every token (row of x)
 // stands in its sequence, and the cache.  Tiles of 256 columns never straddle two of the three ranges
@@ -189,8 +203,9 @@ __device__ __forceinline__ void gt_qkv_epilogue(uint32_t taddr, int col_base, in
 template <typename TOut, int MODE>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, TOut* __restrict__ out,
-               int out_stride, int M, int N, int K, int vec_ok, const GtQkv qkv, int* __restrict__ status) {
-    constexpr bool GATED = MODE == GT_GATED;
+               int out_stride, int M, int N, int K, int vec_ok, const GtQkv qkv, const GtGroups grp, int* __restrict__ status) {
+    constexpr bool GATED = MODE == GT_GATED || MODE == GT_GROUPED_GATED;
+    constexpr bool GROUPED = MODE == GT_GROUPED_GATED || MODE == GT_GROUPED;
     extern __shared__ unsigned char gt_smem_raw[];
     // the swizzled tiles must start on 1024-byte boundaries
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)gt_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -232,6 +247,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             bool stop = false;
             for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x) {
                 const int tm = tile % tiles_m, tn = tile / tiles_m;
+                int w_row = tn * OUT_BN;
+                if (GROUPED) {
+                    const int e = grp.tile_expert[tm];
+                    if (e < 0) continue;
+                    w_row += e * grp.rows_per_expert;
+                }
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % GT_STAGES;
                     if (it >= GT_STAGES && !tc_mbar_wait(&empty_bar[s], ((it / GT_STAGES) - 1) & 1, &gave_up)) {
@@ -245,10 +266,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     tc_mbar_expect(&full_bar[s], GT_STAGE_BYTES);
                     dl_tma_load_2d(a, &tmap_x, kb * GT_BK, tm * GT_BM, &full_bar[s]);
                     if (GATED) {
-                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, tn * OUT_BN, &full_bar[s]);
-                        dl_tma_load_2d(b + GT_B_BYTES / 2, &tmap_w, kb * GT_BK, N + tn * OUT_BN, &full_bar[s]);
+                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, w_row, &full_bar[s]);
+                        dl_tma_load_2d(b + GT_B_BYTES / 2, &tmap_w, kb * GT_BK, w_row + (GROUPED ? grp.up_offset : N), &full_bar[s]);
                     } else {
-                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, tn * GT_BN, &full_bar[s]);
+                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, w_row, &full_bar[s]);
                     }
                 }
             }
@@ -267,7 +288,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const uint32_t idesc = tc_idesc_bf16(GT_BM, GT_BN);
             int it = 0, local = 0;
             bool stop = false;
-            for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x, ++local) {
+            for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x) {
+                if (GROUPED && grp.tile_expert[tile % tiles_m] < 0) continue;
                 const int buf = local & 1;
                 if (local >= 2 && !tc_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &gave_up)) {
                     if (!gave_up) atomicExch(status, 22);
@@ -293,14 +315,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     tc_commit(&empty_bar[s]);                    // the stage is free once these MMAs have read it
                 }
                 if (!stop) tc_commit(&acc_full[buf]);
+                ++local;
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue: warp w reads lanes 32 (w % 4) ..
         const int quarter = warp & 3;
         int local = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int tm = tile % tiles_m, tn = tile / tiles_m;
+            if (GROUPED && grp.tile_expert[tm] < 0) continue;
             const int buf = local & 1;
             // the decision is the warp's: tcgen05.ld below needs all 32 lanes
             const bool ready = tc_mbar_wait(&acc_full[buf], (local >> 1) & 1, &gave_up);
@@ -325,8 +349,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     if (GATED) {
                         float u[32];
                         tc_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
+                        if (GROUPED) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
+                            for (int i = 0; i < 32; ++i) v[i] = dl_gate_value(grp.gate_kind, v[i], u[i], grp.limit, grp.alpha);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
+                        }
                     }
                     if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
                 }
@@ -334,6 +363,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&acc_empty[buf]);
+            ++local;
         }
     }
     tc_fence_before();
@@ -380,8 +410,8 @@ static int gt_tensor_map(CUtensorMap* out, const void* base, long long rows, lon
 
 template <typename TOut, int MODE>
 static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w, void* out, int out_stride, int M, int N, int K,
-                     int blocks, int* status, const GtQkv& qkv = GtQkv{}) {
-    constexpr bool GATED = MODE == GT_GATED;
+                     int blocks, int* status, const GtQkv& qkv = GtQkv{}, const GtGroups& grp = GtGroups{}, int n_experts = 1) {
+    constexpr bool GATED = MODE == GT_GATED || MODE == GT_GROUPED_GATED;
     const size_t smem = (size_t)GT_STAGES * GT_STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -392,7 +422,7 @@ static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w,
     CUtensorMap tmap_x, tmap_w;
     int rc = gt_tensor_map(&tmap_x, x, M, K, (long long)x_stride * 2, GT_BM);
     if (rc != DL_OK) return rc;
-    rc = gt_tensor_map(&tmap_w, w, GATED ? 2ll * N : N, K, (long long)K * 2, GATED ? GT_BN / 2 : GT_BN);
+    rc = gt_tensor_map(&tmap_w, w, (GATED ? 2ll * N : N) * n_experts, K, (long long)K * 2, GATED ? GT_BN / 2 : GT_BN);
     if (rc != DL_OK) return rc;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -403,7 +433,7 @@ static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w,
     if (blocks > n_tiles) blocks = (int)n_tiles;
     const int elem = (int)sizeof(TOut);
     const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)out_stride * elem) % 16 == 0) ? 1 : 0;
-    gemm_tc_kernel<TOut, MODE><<<blocks, GT_THREADS, smem, s>>>(tmap_x, tmap_w, (TOut*)out, out_stride, M, N, K, vec_ok, qkv, status);
+    gemm_tc_kernel<TOut, MODE><<<blocks, GT_THREADS, smem, s>>>(tmap_x, tmap_w, (TOut*)out, out_stride, M, N, K, vec_ok, qkv, grp, status);
     DL_CHECK_LAUNCH("gemm_tc");
     return DL_OK;
 }
@@ -430,6 +460,34 @@ extern "C" int dl_gemm_tc_bf16(const void* x, int x_stride, const void* w, void*
     }
     if (out_dtype == DL_F32) return gt_launch<float, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
     return gt_launch<__nv_bfloat16, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+}
+
+// The products of a feed-forward of experts.  x: bf16 [M, K], the rows sorted by expert and every expert's run padded
+// to whole tiles of 128 rows (M a multiple of 128); tile_expert int32 [M / 128]: the expert of each row tile, -1 for
+// tiles that hold no row.  gated: w is [E, 2N, K] (an expert's N gate rows, then its N up rows) and out bf16 [M, N] =
+// gating(x G_e^T, x U_e^T) with the gating `gate_kind` of gating.cuh; else w is [E, N, K] and out = x W_e^T
+// (float32 or bfloat16).  Rows of padding are computed and written like any other; nobody reads them.
+extern "C" int dl_gemm_tc_grouped_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype, int out_stride,
+                                       int M, int N, int K, int n_experts, const int32_t* tile_expert, int gated, int gate_kind,
+                                       float limit, float alpha, int blocks, int* status, void* stream) {
+    DL_REQUIRE(M >= GT_BM && M % GT_BM == 0 && N >= 1 && K >= 8 && K % 8 == 0 && n_experts >= 1,
+               "gemm_tc_grouped: M=%d (whole tiles of %d rows) N=%d K=%d (a multiple of 8)", M, GT_BM, N, K);
+    DL_REQUIRE(x_stride >= K && x_stride % 8 == 0 && out_stride >= N, "gemm_tc_grouped: row strides");
+    DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tc_grouped: x and W must be 16-byte aligned");
+    DL_REQUIRE(out_dtype == DL_F32 || out_dtype == DL_BF16, "gemm_tc_grouped: out dtype %d", out_dtype);
+    DL_REQUIRE(tile_expert != nullptr && status != nullptr, "gemm_tc_grouped: needs the tiles' experts and a status word");
+    DL_REQUIRE((long long)n_experts * (gated ? 2 : 1) * N < (1ll << 31), "gemm_tc_grouped: too many rows of W");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gated) {
+        DL_REQUIRE(out_dtype == DL_BF16 && gate_kind >= 0 && gate_kind <= 2, "gemm_tc_grouped: the gated product writes bfloat16");
+        const GtGroups grp{tile_expert, 2 * N, N, gate_kind, limit, alpha};
+        return gt_launch<__nv_bfloat16, GT_GROUPED_GATED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp,
+                                                          n_experts);
+    }
+    const GtGroups grp{tile_expert, N, 0, 0, 0.f, 0.f};
+    if (out_dtype == DL_F32)
+        return gt_launch<float, GT_GROUPED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp, n_experts);
+    return gt_launch<__nv_bfloat16, GT_GROUPED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp, n_experts);
 }
 
 // The Q/K/V product of a prompt with the rotation and the cache write in its epilogue.

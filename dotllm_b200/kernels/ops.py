@@ -24,6 +24,10 @@ _library.register_signatures({
     "dl_route_topk": [_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P],
     "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "dl_expert_sort": [_P, _I, _I, _P, _P, _I, _P],
+    "dl_expert_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P],
+    "dl_gemm_tc_grouped_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _F, _I, _P, _P],
 })
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -553,6 +557,55 @@ def expert_down(h, ids, weights, w_down, addend=None):
     out = torch.empty((T, N), dtype=torch.float32, device=h.device)
     _library.call("dl_expert_down", _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_down), _ptr(addend), astride, _ptr(out),
                   _code(h.dtype), T, top, ff, N, E, _stream())
+    return out
+
+
+GROUPED_MIN_ROWS = 128         # (token, choice) rows from which the experts' products run as tensor-core tiles
+EXPERT_TILE = 128              # rows of a tile (EX_TILE in csrc/experts.cu, GT_BM in csrc/gemm_tc.cu)
+
+
+def experts_grouped_takes(x, ids, w_gate_up, w_down):
+    """Do the sorted, tensor-core products take this step's experts?  bfloat16, enough rows to fill tiles, and
+    widths and addresses that the copy engine takes (multiples of 8 values, 16-byte aligned)."""
+    T, top = ids.shape
+    K, ff = w_gate_up.shape[2], w_down.shape[2]
+    return (x.dtype == torch.bfloat16 and T * top >= GROUPED_MIN_ROWS and K % 8 == 0 and ff % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
+
+
+def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1.0, addend=None):
+    """The same result as ``expert_gate_up`` followed by ``expert_down``, for many rows: the (token, choice) rows are
+    sorted by expert on the device, each expert's run padded to whole tiles, and the two products run on the tensor
+    cores (tcgen05) with the gating in the first one's epilogue; a last kernel sums every token's choices with
+    their weights (and the addend).  Shapes depend only on the step's sizes, never on the choice."""
+    _need_cuda(x, ids, weights, w_gate_up, w_down, addend)
+    _int32(ids, "expert ids")
+    T, top = ids.shape
+    E, two_ff, K = w_gate_up.shape
+    ff, N = two_ff // 2, w_down.shape[1]
+    rows = T * top
+    tiles = (rows + EXPERT_TILE - 1) // EXPERT_TILE + E - 1          # every expert may end in a tile that is not full
+    dev = x.device
+    place = torch.empty(rows, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+    _library.call("dl_expert_sort", _ptr(ids), rows, E, _ptr(place), _ptr(tile_expert), tiles, _stream())
+    sorted_x = torch.empty((tiles * EXPERT_TILE, K), dtype=torch.bfloat16, device=dev)
+    _library.call("dl_expert_gather", _ptr(x), x.stride(0) if T > 1 else K, _ptr(place), _ptr(sorted_x), rows, top, K, _stream())
+    status = _library.status_word(dev).data_ptr()
+    h = torch.empty((tiles * EXPERT_TILE, ff), dtype=torch.bfloat16, device=dev)
+    _library.call("dl_gemm_tc_grouped_bf16", _ptr(sorted_x), K, _ptr(w_gate_up), _ptr(h), 1, ff, tiles * EXPERT_TILE, ff, K, E,
+                  _ptr(tile_expert), 1, GATINGS[kind], float(limit), float(alpha), 0, status, _stream())
+    y = torch.empty((tiles * EXPERT_TILE, N), dtype=torch.float32, device=dev)
+    _library.call("dl_gemm_tc_grouped_bf16", _ptr(h), ff, _ptr(w_down), _ptr(y), 0, N, tiles * EXPERT_TILE, N, ff, E,
+                  _ptr(tile_expert), 0, 0, 0.0, 0.0, 0, status, _stream())
+    astride = 0
+    if addend is not None:
+        astride = _rows_view(addend, "expert addend")
+        if addend.dtype != torch.float32 or addend.shape != (T, N):
+            raise KernelError("experts_grouped: the addend must be float32 [T, N]")
+    out = torch.empty((T, N), dtype=torch.float32, device=dev)
+    _library.call("dl_expert_combine", _ptr(y), N, _ptr(place), _ptr(weights), _ptr(addend), astride, _ptr(out), T, top, N, _stream())
     return out
 
 

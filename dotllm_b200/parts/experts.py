@@ -84,12 +84,16 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x):
         ids, weights = ops.route_topk(x, self.w_router, self.b_router, self.top)
-        h = ops.expert_gate_up(x, ids, self.w_gate_up, self.activation, self.limit, self.alpha)
         shared = None
         if self.shared_ff:
             s = ops.gated_activation(ops.linear(x, self.ws_gate_up, resident=True), self.activation, self.shared_limit,
                                      self.alpha)
             shared = ops.linear(s, self.ws_down, out_dtype=torch.float32, resident=True)
+        if ops.experts_grouped_takes(x, ids, self.w_gate_up, self.w_down):
+            # many rows: sorted by expert, both products as tensor-core tiles
+            return ops.experts_grouped(x, ids, weights, self.w_gate_up, self.w_down, self.activation, self.limit, self.alpha,
+                                       addend=shared)
+        h = ops.expert_gate_up(x, ids, self.w_gate_up, self.activation, self.limit, self.alpha)
         return ops.expert_down(h, ids, weights, self.w_down, addend=shared)
 
 

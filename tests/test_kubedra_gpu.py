@@ -185,6 +185,38 @@ def test_head_norm_router_experts_and_branch_norm_kernels(dtype):
     assert torch.equal(got.cpu(), table[ids_.long()].float() + pos[at.long()].float())
 
 
+@pytest.mark.parametrize("T,K,ff,E,top", [(300, 72, 40, 6, 2), (64, 256, 136, 5, 3), (1000, 64, 264, 3, 1)])
+def test_experts_sorted_into_tensor_core_tiles(T, K, ff, E, top):
+    """Many rows: the sorted tcgen05 path against the row-by-row kernels and the plain expert, with an expert that
+    nobody chooses, runs that do not fill their last tile, and widths that are not multiples of a tile."""
+    dtype = torch.bfloat16
+    gen = torch.Generator().manual_seed(T)
+    x = g64(T, K, seed=1).to(dtype)
+    ids = torch.stack([torch.randperm(E - 1, generator=gen)[:top] for _ in range(T)]).to(torch.int32)
+    ids[ids >= 1] += 1                                              # expert 1 is never chosen
+    wts = torch.softmax(g64(T, top, seed=2), -1).float()
+    w = {}
+    for e in range(E):
+        w[f"m.e{e}.gate"], w[f"m.e{e}.up"] = g64(ff, K, seed=10 + e, scale=0.3).to(dtype), g64(ff, K, seed=30 + e, scale=0.3).to(dtype)
+        w[f"m.e{e}.down"] = g64(K, ff, seed=50 + e, scale=0.2).to(dtype)
+    w_gu = torch.stack([torch.cat([w[f"m.e{e}.gate"], w[f"m.e{e}.up"]]) for e in range(E)]).to(DEV)
+    w_d = torch.stack([w[f"m.e{e}.down"] for e in range(E)]).to(DEV)
+    addend = g64(T, K, seed=3).float()
+    xd, idd, wd_ = x.to(DEV), ids.to(DEV), wts.to(DEV)
+    assert ops.experts_grouped_takes(xd, idd, w_gu, w_d)
+    got = ops.experts_grouped(xd, idd, wd_, w_gu, w_d, "clamped_sigmoid", 1.5, 1.702, addend=addend.to(DEV))
+    rowwise = ops.expert_down(ops.expert_gate_up(xd, idd, w_gu, "clamped_sigmoid", 1.5, 1.702), idd, wd_, w_d, addend.to(DEV))
+    want = addend.double().clone()
+    wf = {k: v.double() for k, v in w.items()}
+    for t in range(0, T, 7):
+        for e, gw in zip(ids[t].tolist(), wts[t].tolist()):
+            want[t] += gw * pk.clamped_expert(x[t:t + 1].double(), wf, f"m.e{e}.", 1.5)[0]
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got.cpu().double()[::7], want[::7], rtol=2e-2, atol=2e-2)
+    assert torch.allclose(got, rowwise, rtol=1e-2, atol=1e-2)        # both round the gated activations to bfloat16 once
+    assert torch.equal(got, ops.experts_grouped(xd, idd, wd_, w_gu, w_d, "clamped_sigmoid", 1.5, 1.702, addend=addend.to(DEV)))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T", [3, 50])
 def test_products_per_head(T, dtype):
