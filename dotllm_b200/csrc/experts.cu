@@ -5,8 +5,8 @@
 //   expert:  y = D_e act(G_e x, U_e x)       (act: one of the gatings of gating.cuh)
 //   output:  sum over the chosen experts of weight * y   (+ an addend per token, e.g. a shared expert)
 //
-// Three kernels, none of which needs the host to know which experts were chosen (a step can be
-// captured in a graph): the router (a warp per token), the gated product (a block per (token, chosen
+// Kernels, none of which needs the host to know which experts were chosen (a step can be captured in
+// a graph): the choice (a warp per token, from the float32 logits of the router's product), the gated product (a block per (token, chosen
 // expert) row, a warp per output: the row's activations wait in shared memory as float32 and every
 // lane walks its share of the expert's weight row), and the down product with the weighted sum in
 // it (a block per token).  Every output is one warp's sum in an order that depends only on the sizes,
@@ -17,10 +17,10 @@
 #define EX_WARPS 8
 #define EX_OUT_PER_BLOCK 64
 
-template <typename T>
+// logits float32 [rows, E] (the router's product), bias float32 [E] or NULL.  A warp per row.
 __global__ void __launch_bounds__(32 * EX_WARPS)
-route_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ wr, const float* __restrict__ bias,
-                  int32_t* __restrict__ ids, float* __restrict__ weights, int rows, int K, int E, int top) {
+route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ bias, int32_t* __restrict__ ids,
+                  float* __restrict__ weights, int rows, int E, int top) {
     extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -29,14 +29,7 @@ route_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ w
     if (row >= rows) return;                          // warps are independent below
     float* logits = route_smem + (size_t)warp * (E + top);
     float* chosen = logits + E;
-    const T* xr = x + (size_t)row * x_stride;
-    for (int e = 0; e < E; ++e) {
-        const T* w = wr + (size_t)e * K;
-        float acc = 0.f;
-        for (int c = lane; c < K; c += 32) acc += dl_to_f32<T>(xr[c]) * dl_to_f32<T>(w[c]);
-        acc = dl_warp_sum(acc);
-        if (lane == 0) logits[e] = acc + (bias != nullptr ? bias[e] : 0.f);
-    }
+    for (int e = lane; e < E; e += 32) logits[e] = z[(size_t)row * z_stride + e] + (bias != nullptr ? bias[e] : 0.f);
     __syncwarp();
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
@@ -66,26 +59,62 @@ route_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ w
     }
 }
 
-// x [rows, K] of dtype; wr [E, K] of dtype; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
-extern "C" int dl_route_topk(const void* x, int x_stride, const void* wr, const float* bias, int dtype, int32_t* ids,
-                             float* weights, int rows, int K, int E, int top, void* stream) {
-    DL_REQUIRE(rows >= 0 && K > 0 && E > 0 && top > 0 && top <= E && x_stride >= K, "route_topk: bad sizes E=%d top=%d", E, top);
+// z float32 [rows, E], rows z_stride apart; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
+extern "C" int dl_route_topk(const float* z, int z_stride, const float* bias, int32_t* ids, float* weights, int rows, int E,
+                             int top, void* stream) {
+    DL_REQUIRE(rows >= 0 && E > 0 && top > 0 && top <= E && z_stride >= E, "route_topk: bad sizes E=%d top=%d", E, top);
     const size_t smem = (size_t)EX_WARPS * (E + top) * sizeof(float);
     DL_REQUIRE(smem <= 48 * 1024, "route_topk: %d experts are more than the kernel's shared memory takes", E);
     if (rows == 0) return DL_OK;
-    cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((rows + EX_WARPS - 1) / EX_WARPS), block(32 * EX_WARPS);
-    cudaError_t e;
-    if (dtype == DL_F32)
-        e = dl_launch_dependent(route_topk_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, (const float*)wr, bias,
-                                ids, weights, rows, K, E, top);
-    else if (dtype == DL_BF16)
-        e = dl_launch_dependent(route_topk_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride,
-                                (const __nv_bfloat16*)wr, bias, ids, weights, rows, K, E, top);
-    else
-        return dl_fail(DL_ERR_UNSUPPORTED, "route_topk: dtype %d", dtype);
+    cudaError_t e = dl_launch_dependent(route_topk_kernel, grid, block, smem, (cudaStream_t)stream, z, z_stride, bias, ids, weights,
+                                        rows, E, top);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "route_topk: %s", cudaGetErrorString(e));
     return DL_OK;
+}
+
+// A warp's dot product of a weight row with activations that wait in shared memory as float32.  With `vec` every
+// lane takes 16 bytes of the row at a time (the caller has checked the rows' width and address), and the activations
+// lie permuted so that the values the 32 lanes need at one time fall into 32 different banks: within each run of
+// 32 * N values, value c sits at (c % N) * 32 + c / N (N values a lane, ex_place).  Without `vec`, as they come.
+template <typename T> struct ExVec;
+template <> struct ExVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ float dot(const float* w, const float* x) {
+        const float4 a = *reinterpret_cast<const float4*>(w);
+        return a.x * x[0] + a.y * x[32] + a.z * x[64] + a.w * x[96];
+    }
+};
+template <> struct ExVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ float dot(const __nv_bfloat16* w, const float* x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(w);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc += __low2float(p[i]) * x[64 * i] + __high2float(p[i]) * x[64 * i + 32];
+        return acc;
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ int ex_place(int c, bool vec) {
+    constexpr int N = ExVec<T>::N, RUN = 32 * ExVec<T>::N;
+    return vec ? (c / RUN) * RUN + (c % N) * 32 + (c % RUN) / N : c;
+}
+// floats of shared memory that K staged activations take (whole runs when permuted)
+static inline size_t ex_staged(int K, int n_per_lane) { return (size_t)((K + 32 * n_per_lane - 1) / (32 * n_per_lane)) * 32 * n_per_lane; }
+
+template <typename T>
+__device__ __forceinline__ float ex_row_dot(const T* __restrict__ w, const float* __restrict__ x, int K, int lane, bool vec) {
+    float acc = 0.f;
+    if (vec) {
+        constexpr int N = ExVec<T>::N;
+        for (int c = lane * N; c < K; c += 32 * N) acc += ExVec<T>::dot(w + c, x + (c - lane * N) + lane);
+    } else {
+        for (int c = lane; c < K; c += 32) acc += x[c] * dl_to_f32<T>(w[c]);
+    }
+    return dl_warp_sum(acc);
 }
 
 // Row r = (token r / top, chosen expert ids[r]):  out[r, n] = act(G_e[n, :] . x[token], U_e[n, :] . x[token]).
@@ -93,14 +122,14 @@ extern "C" int dl_route_topk(const void* x, int x_stride, const void* wr, const 
 template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __restrict__ ids, const T* __restrict__ w,
-                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha) {
+                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha, int vec) {
     extern __shared__ float ex_x[];                  // [K]
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* xr = x + (size_t)(r / top) * x_stride;
-    for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[c] = dl_to_f32<T>(xr[c]);
+    for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[ex_place<T>(c, vec != 0)] = dl_to_f32<T>(xr[c]);
     __syncthreads();
     const int e = ids[r];
     const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
@@ -110,14 +139,8 @@ expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __re
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
         const T* gr = we + (size_t)n * K;
         const T* ur = we + (size_t)(ff + n) * K;
-        float g = 0.f, u = 0.f;
-        for (int c = lane; c < K; c += 32) {
-            const float xv = ex_x[c];
-            g += xv * dl_to_f32<T>(gr[c]);
-            u += xv * dl_to_f32<T>(ur[c]);
-        }
-        g = dl_warp_sum(g);
-        u = dl_warp_sum(u);
+        const float g = ex_row_dot<T>(gr, ex_x, K, lane, vec != 0);
+        const float u = ex_row_dot<T>(ur, ex_x, K, lane, vec != 0);
         if (lane == 0) out[(size_t)r * ff + n] = dl_from_f32<T>(ok ? dl_gate_value(kind, g, u, limit, alpha) : 0.f);
     }
 }
@@ -126,18 +149,19 @@ extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids
                                  int tokens, int top, int K, int ff, int E, int kind, float limit, float alpha, void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && K > 0 && ff > 0 && E > 0 && x_stride >= K && kind >= 0 && kind <= 2,
                "expert_gate_up: bad arguments");
-    DL_REQUIRE((size_t)K * sizeof(float) <= 48 * 1024, "expert_gate_up: rows of %d values are more than the kernel takes", K);
+    DL_REQUIRE(ex_staged(K, 8) * sizeof(float) <= 48 * 1024, "expert_gate_up: rows of %d values are more than the kernel takes", K);
     if (tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tokens * top, (ff + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
-    const size_t smem = (size_t)K * sizeof(float);
+    const size_t smem = ex_staged(K, 8) * sizeof(float);
+    const int vec = (K % 8 == 0 && ((uintptr_t)w % 16) == 0) ? 1 : 0;      // every weight row starts on a 16-byte boundary
     cudaError_t e;
     if (dtype == DL_F32)
         e = dl_launch_dependent(expert_gate_up_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, ids, (const float*)w,
-                                (float*)out, top, K, ff, E, kind, limit, alpha);
+                                (float*)out, top, K, ff, E, kind, limit, alpha, vec);
     else if (dtype == DL_BF16)
         e = dl_launch_dependent(expert_gate_up_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride, ids,
-                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha);
+                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha, vec);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_gate_up: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gate_up: %s", cudaGetErrorString(e));
@@ -150,14 +174,18 @@ template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, const float* __restrict__ weights,
                    const T* __restrict__ w, const float* __restrict__ addend, int addend_stride, float* __restrict__ out,
-                   int top, int ff, int N, int E) {
+                   int top, int ff, int N, int E, int vec) {
     extern __shared__ float ex_h[];                  // [top][ff]
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* hr = h + (size_t)t * top * ff;
-    for (int c = threadIdx.x; c < top * ff; c += blockDim.x) ex_h[c] = dl_to_f32<T>(hr[c]);
+    const int staged = vec ? (ff + 32 * ExVec<T>::N - 1) / (32 * ExVec<T>::N) * 32 * ExVec<T>::N : ff;     // per choice
+    for (int c = threadIdx.x; c < top * ff; c += blockDim.x) {
+        const int j = c / ff;
+        ex_h[(size_t)j * staged + ex_place<T>(c - j * ff, vec != 0)] = dl_to_f32<T>(hr[c]);
+    }
     __syncthreads();
     const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
     const int n1 = min(N, n0 + EX_OUT_PER_BLOCK);
@@ -167,11 +195,8 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
             const int e = ids[(size_t)t * top + j];
             if (e < 0 || e >= E) continue;
             const T* wr = w + ((size_t)e * N + n) * ff;
-            const float* hj = ex_h + (size_t)j * ff;
-            float acc = 0.f;
-            for (int c = lane; c < ff; c += 32) acc += hj[c] * dl_to_f32<T>(wr[c]);
-            acc = dl_warp_sum(acc);
-            total += weights[(size_t)t * top + j] * acc;
+            const float* hj = ex_h + (size_t)j * staged;
+            total += weights[(size_t)t * top + j] * ex_row_dot<T>(wr, hj, ff, lane, vec != 0);
         }
         if (lane == 0) out[(size_t)t * N + n] = total + (addend != nullptr ? addend[(size_t)t * addend_stride + n] : 0.f);
     }
@@ -181,21 +206,23 @@ extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* we
                               int addend_stride, float* out, int dtype, int tokens, int top, int ff, int N, int E,
                               void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && N > 0 && E > 0, "expert_down: bad sizes");
-    DL_REQUIRE((size_t)top * ff * sizeof(float) <= 96 * 1024, "expert_down: %d x %d activations are more than the kernel takes", top, ff);
+    DL_REQUIRE((size_t)top * ex_staged(ff, 8) * sizeof(float) <= 96 * 1024, "expert_down: %d x %d activations are more than the kernel takes",
+               top, ff);
     if (tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tokens, (N + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
-    const size_t smem = (size_t)top * ff * sizeof(float);
+    const size_t smem = (size_t)top * ex_staged(ff, 8) * sizeof(float);
+    const int vec = (ff % 8 == 0 && ((uintptr_t)w % 16) == 0) ? 1 : 0;
     cudaError_t e;
     if (dtype == DL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<float>, grid, block, smem, s, (const float*)h, ids, weights, (const float*)w,
-                                addend, addend_stride, out, top, ff, N, E);
+                                addend, addend_stride, out, top, ff, N, E, vec);
     } else if (dtype == DL_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(expert_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, ids, weights,
-                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E);
+                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec);
     } else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_down: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));

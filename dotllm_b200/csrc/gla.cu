@@ -13,16 +13,23 @@
 // holds and leaving the new state there: a prompt, a part of a prompt and a single decoded token are
 // the same loop, so a position's result does not depend on how its sequence was cut into steps.  A
 // block owns GLA_COLS value channels of one (sequence, head): columns of S never mix, so blocks need
-// nothing from each other.  GLA_SPLIT neighbouring lanes share a column, each holding every
-// GLA_SPLIT-th key channel of it in registers; their partial sums of o meet by shuffles.  The token's
-// q, k and decays are staged in shared memory (two buffers, one barrier per token) while the loads
-// of the next token are in flight.
+// nothing from each other.  GLA_SPLIT neighbouring lanes share a column, each holding a run of ROWS
+// key channels of it in registers.  Tokens are staged in shared memory a batch at a time (two
+// buffers; while a batch is walked the loads of the next one are in flight), rows padded with zeros
+// to GLA_SPLIT * ROWS channels so that the walk needs no test and reads its q, k and decays 16 bytes
+// at a time.  Per token a thread does its ROWS multiply-adds on the state and on its share of o and
+// leaves that share in shared memory; the shares of a batch are summed afterwards, all tokens at
+// once, so nothing in the walk waits for another lane.
 #include "common.cuh"
 
-#define GLA_COLS 32
-#define GLA_SPLIT 8
+#define GLA_COLS 16
+#define GLA_SPLIT 16
 #define GLA_THREADS (GLA_COLS * GLA_SPLIT)
 #define GLA_MAX_DIM GLA_THREADS          // key channels per head that the scan takes
+#define GLA_STAGE 1024                   // values of q (and of k, and of the decays) staged per batch
+#define GLA_MAX_BATCH 16                 // tokens per batch at most
+#define GLA_LOADS (GLA_STAGE / GLA_THREADS)
+#define GLA_VLOADS (GLA_MAX_BATCH * GLA_COLS / GLA_THREADS)
 
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(GLA_THREADS)
@@ -31,12 +38,17 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 const int32_t* __restrict__ cu_new, const int32_t* __restrict__ slots, float* __restrict__ state,
                 int n_slots, float* __restrict__ out, int out_stride, int H, int dim, int vdim, float q_scale,
                 float inv_tau) {
-    __shared__ float sq[2][GLA_MAX_DIM], sk[2][GLA_MAX_DIM], sa[2][GLA_MAX_DIM];
+    constexpr int PAD = GLA_SPLIT * ROWS;                       // staged channels per token, >= dim
+    constexpr int BATCH = GLA_STAGE / PAD < GLA_MAX_BATCH ? GLA_STAGE / PAD : GLA_MAX_BATCH;
+    __shared__ __align__(16) float sq[2][GLA_STAGE], sk[2][GLA_STAGE], sa[2][GLA_STAGE];
+    __shared__ float sv[2][GLA_MAX_BATCH * GLA_COLS];
+    __shared__ __align__(16) float sp[GLA_MAX_BATCH * GLA_COLS * GLA_SPLIT];     // every lane's share of o, per (token, column)
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int b = blockIdx.z, h = blockIdx.y;
-    const int tid = threadIdx.x, r = tid % GLA_SPLIT;
-    const int col = blockIdx.x * GLA_COLS + tid / GLA_SPLIT;
+    const int tid = threadIdx.x, r = tid % GLA_SPLIT, c_local = tid / GLA_SPLIT;
+    const int col0 = blockIdx.x * GLA_COLS;
+    const int col = col0 + c_local;
     const bool col_ok = col < vdim;
     const int t0 = cu_new[b], t1 = cu_new[b + 1];
     const int slot = slots[b];
@@ -45,59 +57,93 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     float s[ROWS];
 #pragma unroll
     for (int m = 0; m < ROWS; ++m) {
-        const int i = r + GLA_SPLIT * m;
-        s[m] = (i < dim && col_ok) ? S[(size_t)i * vdim + col] : 0.f;
+        const int ch = r * ROWS + m;
+        s[m] = (ch < dim && col_ok) ? S[(size_t)ch * vdim + col] : 0.f;
     }
-    float rq = 0.f, rk = 0.f, rz = 0.f, rv = 0.f;
-    const bool loader = tid < dim;
-    {
-        const size_t row = (size_t)t0;
-        if (loader) {
-            rq = dl_to_f32<T>(q[row * ld + h * dim + tid]);
-            rk = dl_to_f32<T>(k[row * ld + h * dim + tid]);
-            rz = z[row * z_stride + h * dim + tid] + z_bias[h * dim + tid];
-        }
-        if (col_ok) rv = dl_to_f32<T>(v[row * ld + h * vdim + col]);
-    }
-    int buf = 0;
-    for (int t = t0; t < t1; ++t) {
-        if (loader) {
-            sq[buf][tid] = rq * q_scale;
-            sk[buf][tid] = rk;
-            const float log_sigmoid = fminf(rz, 0.f) - log1pf(expf(-fabsf(rz)));
-            sa[buf][tid] = expf(log_sigmoid * inv_tau);
-        }
-        const float vt = rv;
-        __syncthreads();
-        if (t + 1 < t1) {
-            const size_t row = (size_t)(t + 1);
-            if (loader) {
-                rq = dl_to_f32<T>(q[row * ld + h * dim + tid]);
-                rk = dl_to_f32<T>(k[row * ld + h * dim + tid]);
-                rz = z[row * z_stride + h * dim + tid] + z_bias[h * dim + tid];
-            }
-            if (col_ok) rv = dl_to_f32<T>(v[row * ld + h * vdim + col]);
-        }
-        float o = 0.f;
+    // What a thread fetches for the next batch stays in registers as it was loaded: converting or adding here would
+    // make the fetch wait for its own loads, and the walk of the present batch behind it.  Every load is from a valid
+    // address (clamped), so that none hides behind a branch; what lies outside the batch is dropped when it is staged.
+    T rq[GLA_LOADS], rk[GLA_LOADS], rv[GLA_VLOADS];
+    float rz[GLA_LOADS], rb[GLA_LOADS];
+    // element e of a batch is (token e / PAD, key channel e % PAD); value e is (token e / GLA_COLS, column e % GLA_COLS)
+    auto fetch = [&](int first, int count) {
 #pragma unroll
-        for (int m = 0; m < ROWS; ++m) {
-            const int i = r + GLA_SPLIT * m;
-            if (i < dim) {
-                s[m] = sa[buf][i] * s[m] + sk[buf][i] * vt;
-                o += s[m] * sq[buf][i];
+        for (int l = 0; l < GLA_LOADS; ++l) {
+            const int e = tid + GLA_THREADS * l;
+            const int tok = min(e / PAD, count - 1), ch = min(e % PAD, dim - 1);
+            const size_t row = (size_t)(first + tok);
+            rq[l] = q[row * ld + h * dim + ch];
+            rk[l] = k[row * ld + h * dim + ch];
+            rz[l] = z[row * z_stride + h * dim + ch];
+            rb[l] = z_bias[h * dim + ch];
+        }
+#pragma unroll
+        for (int l = 0; l < GLA_VLOADS; ++l) {
+            const int e = tid + GLA_THREADS * l;
+            const int tok = min(e / GLA_COLS, count - 1), c = min(col0 + e % GLA_COLS, vdim - 1);
+            rv[l] = v[(size_t)(first + tok) * ld + h * vdim + c];
+        }
+    };
+    fetch(t0, min(BATCH, t1 - t0));
+    int buf = 0;
+    for (int first = t0; first < t1; first += BATCH) {
+        const int count = min(BATCH, t1 - first);
+#pragma unroll
+        for (int l = 0; l < GLA_LOADS; ++l) {
+            const int e = tid + GLA_THREADS * l;
+            if (e < BATCH * PAD) {
+                const bool live = e / PAD < count && e % PAD < dim;    // a padded channel decays to nothing and adds nothing
+                const float zz = rz[l] + rb[l];
+                const float log_sigmoid = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+                sq[buf][e] = live ? dl_to_f32<T>(rq[l]) * q_scale : 0.f;
+                sk[buf][e] = live ? dl_to_f32<T>(rk[l]) : 0.f;
+                sa[buf][e] = live ? expf(log_sigmoid * inv_tau) : 0.f;
             }
         }
-        o += __shfl_xor_sync(0xffffffffu, o, 1);
-        o += __shfl_xor_sync(0xffffffffu, o, 2);
-        o += __shfl_xor_sync(0xffffffffu, o, 4);
-        if (r == 0 && col_ok) out[(size_t)t * out_stride + h * vdim + col] = o;
+#pragma unroll
+        for (int l = 0; l < GLA_VLOADS; ++l) sv[buf][tid + GLA_THREADS * l] = dl_to_f32<T>(rv[l]);
+        __syncthreads();                                        // the batch is staged; the shares of the batch before are summed
+        if (first + BATCH < t1) fetch(first + BATCH, min(BATCH, t1 - first - BATCH));
+#pragma unroll 4
+        for (int i = 0; i < count; ++i) {                      // tokens depend on each other through s alone: their loads and sums overlap
+            const float vt = sv[buf][i * GLA_COLS + c_local];
+            const float4* aq = reinterpret_cast<const float4*>(sq[buf] + i * PAD + r * ROWS);
+            const float4* ak = reinterpret_cast<const float4*>(sk[buf] + i * PAD + r * ROWS);
+            const float4* aa = reinterpret_cast<const float4*>(sa[buf] + i * PAD + r * ROWS);
+            float o = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int m = 0; m < ROWS / 4; ++m) {
+                const float4 a4 = aa[m], k4 = ak[m], q4 = aq[m];
+                s[4 * m] = a4.x * s[4 * m] + k4.x * vt;
+                s[4 * m + 1] = a4.y * s[4 * m + 1] + k4.y * vt;
+                s[4 * m + 2] = a4.z * s[4 * m + 2] + k4.z * vt;
+                s[4 * m + 3] = a4.w * s[4 * m + 3] + k4.w * vt;
+                o += s[4 * m] * q4.x;
+                o1 += s[4 * m + 1] * q4.y;
+                o2 += s[4 * m + 2] * q4.z;
+                o3 += s[4 * m + 3] * q4.w;
+            }
+            sp[(i * GLA_COLS + c_local) * GLA_SPLIT + r] = (o + o1) + (o2 + o3);
+        }
+        __syncthreads();
+        for (int e = tid; e < count * GLA_COLS; e += GLA_THREADS) {
+            const float4* part = reinterpret_cast<const float4*>(sp + e * GLA_SPLIT);
+            float total = 0.f;
+#pragma unroll
+            for (int p4 = 0; p4 < GLA_SPLIT / 4; ++p4) {
+                const float4 x4 = part[p4];
+                total += (x4.x + x4.y) + (x4.z + x4.w);
+            }
+            const int c = col0 + e % GLA_COLS;
+            if (c < vdim) out[(size_t)(first + e / GLA_COLS) * out_stride + h * vdim + c] = total;
+        }
         buf ^= 1;
     }
     if (col_ok) {
 #pragma unroll
         for (int m = 0; m < ROWS; ++m) {
-            const int i = r + GLA_SPLIT * m;
-            if (i < dim) S[(size_t)i * vdim + col] = s[m];
+            const int ch = r * ROWS + m;
+            if (ch < dim) S[(size_t)ch * vdim + col] = s[m];
         }
     }
 }
@@ -115,8 +161,7 @@ static int launch_scan(const void* q, const void* k, const void* v, int ld, cons
                             q_scale, inv_tau)
     if (rows <= 4) GLA_LAUNCH(4);
     else if (rows <= 8) GLA_LAUNCH(8);
-    else if (rows <= 16) GLA_LAUNCH(16);
-    else GLA_LAUNCH(32);
+    else GLA_LAUNCH(16);
 #undef GLA_LAUNCH
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gla_scan: %s", cudaGetErrorString(e));
     return DL_OK;

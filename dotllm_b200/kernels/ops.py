@@ -21,7 +21,7 @@ _library.register_signatures({
     "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
     "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-    "dl_route_topk": [_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
     "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "dl_expert_sort": [_P, _I, _I, _P, _P, _I, _P],
@@ -505,7 +505,6 @@ def route_topk(x, w_router, bias, top):
     """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and the
     softmax over the chosen logits alone.  Returns (ids int32 [T, top], weights float32 [T, top])."""
     _need_cuda(x, w_router, bias)
-    xs = _rows_view(x, "route x")
     E, K = w_router.shape
     if x.shape[1] != K or x.dtype != w_router.dtype or not w_router.is_contiguous():
         raise KernelError(f"route_topk: x {tuple(x.shape)} does not match the router {tuple(w_router.shape)}")
@@ -514,10 +513,10 @@ def route_topk(x, w_router, bias, top):
     if not 0 < top <= E:
         raise KernelError(f"route_topk: cannot choose {top} of {E} experts")
     T = x.shape[0]
+    z = linear(x, w_router, out_dtype=torch.float32, resident=True)         # float32 accumulation, float32 logits
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    _library.call("dl_route_topk", _ptr(x), xs, _ptr(w_router), _ptr(bias), _code(x.dtype), _ptr(ids), _ptr(weights),
-                  T, K, E, top, _stream())
+    _library.call("dl_route_topk", _ptr(z), z.stride(0) if T > 1 else E, _ptr(bias), _ptr(ids), _ptr(weights), T, E, top, _stream())
     return ids, weights
 
 
