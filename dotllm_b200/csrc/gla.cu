@@ -13,7 +13,7 @@
 // holds and leaving the new state there: a prompt, a part of a prompt and a single decoded token are
 // the same loop, so a position's result does not depend on how its sequence was cut into steps.  A
 // block owns GLA_COLS value channels of one (sequence, head): columns of S never mix, so blocks need
-// nothing from each other.  GLA_SPLIT neighbouring lanes share a column, each holding a run of ROWS
+// nothing from each other.  GLA_SPLIT threads share a column, each holding a run of ROWS
 // key channels of it in registers.  Tokens are staged in shared memory a batch at a time (two
 // buffers; while a batch is walked the loads of the next one are in flight), rows padded with zeros
 // to GLA_SPLIT * ROWS channels so that the walk needs no test and reads its q, k and decays 16 bytes
@@ -28,25 +28,30 @@
 #define GLA_MAX_DIM GLA_THREADS          // key channels per head that the scan takes
 #define GLA_STAGE 1024                   // values of q (and of k, and of the decays) staged per batch
 #define GLA_MAX_BATCH 16                 // tokens per batch at most
-#define GLA_LOADS (GLA_STAGE / GLA_THREADS)
-#define GLA_VLOADS (GLA_MAX_BATCH * GLA_COLS / GLA_THREADS)
 
-template <typename T, int ROWS>
-__global__ void __launch_bounds__(GLA_THREADS)
+// SINGLE: every sequence of the step brings one token (a decode step).  The same arithmetic in the same order, so the
+// same bits; only the staging shrinks to one token, which leaves room for more blocks on a multiprocessor - a decode
+// step is thousands of short blocks, each a chain of dependent latencies, and only their number in flight hides those.
+template <typename T, int ROWS, bool SINGLE>
+__global__ void __launch_bounds__(GLA_THREADS, SINGLE && ROWS <= 8 ? 5 : 1)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
                 const float* __restrict__ z, int z_stride, const float* __restrict__ z_bias,
                 const int32_t* __restrict__ cu_new, const int32_t* __restrict__ slots, float* __restrict__ state,
                 int n_slots, float* __restrict__ out, int out_stride, int H, int dim, int vdim, float q_scale,
                 float inv_tau) {
     constexpr int PAD = GLA_SPLIT * ROWS;                       // staged channels per token, >= dim
-    constexpr int BATCH = GLA_STAGE / PAD < GLA_MAX_BATCH ? GLA_STAGE / PAD : GLA_MAX_BATCH;
-    __shared__ __align__(16) float sq[2][GLA_STAGE], sk[2][GLA_STAGE], sa[2][GLA_STAGE];
-    __shared__ float sv[2][GLA_MAX_BATCH * GLA_COLS];
-    __shared__ __align__(16) float sp[GLA_MAX_BATCH * GLA_COLS * GLA_SPLIT];     // every lane's share of o, per (token, column)
+    constexpr int BATCH = SINGLE ? 1 : (GLA_STAGE / PAD < GLA_MAX_BATCH ? GLA_STAGE / PAD : GLA_MAX_BATCH);
+    constexpr int GLA_LOADS = (BATCH * PAD + GLA_THREADS - 1) / GLA_THREADS;
+    constexpr int GLA_VLOADS = (BATCH * GLA_COLS + GLA_THREADS - 1) / GLA_THREADS;
+    __shared__ __align__(16) float sq[2][BATCH * PAD], sk[2][BATCH * PAD], sa[2][BATCH * PAD];
+    __shared__ float sv[2][GLA_VLOADS * GLA_THREADS];
+    __shared__ __align__(16) float sp[BATCH * GLA_COLS * GLA_SPLIT];     // every lane's share of o, per (token, column)
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int b = blockIdx.z, h = blockIdx.y;
-    const int tid = threadIdx.x, r = tid % GLA_SPLIT, c_local = tid / GLA_SPLIT;
+    // neighbouring lanes hold neighbouring columns: the state's rows are read and written in runs of GLA_COLS values,
+    // and a warp reads only two places of the staged q, k and decays at a time
+    const int tid = threadIdx.x, r = tid / GLA_COLS, c_local = tid % GLA_COLS;
     const int col0 = blockIdx.x * GLA_COLS;
     const int col = col0 + c_local;
     const bool col_ok = col < vdim;
@@ -123,17 +128,15 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 o2 += s[4 * m + 2] * q4.z;
                 o3 += s[4 * m + 3] * q4.w;
             }
-            sp[(i * GLA_COLS + c_local) * GLA_SPLIT + r] = (o + o1) + (o2 + o3);
+            sp[(i * GLA_SPLIT + r) * GLA_COLS + c_local] = (o + o1) + (o2 + o3);
         }
         __syncthreads();
         for (int e = tid; e < count * GLA_COLS; e += GLA_THREADS) {
-            const float4* part = reinterpret_cast<const float4*>(sp + e * GLA_SPLIT);
+            const float* part = sp + (e / GLA_COLS) * GLA_SPLIT * GLA_COLS + e % GLA_COLS;
             float total = 0.f;
 #pragma unroll
-            for (int p4 = 0; p4 < GLA_SPLIT / 4; ++p4) {
-                const float4 x4 = part[p4];
-                total += (x4.x + x4.y) + (x4.z + x4.w);
-            }
+            for (int p4 = 0; p4 < GLA_SPLIT; p4 += 4)
+                total += (part[p4 * GLA_COLS] + part[(p4 + 1) * GLA_COLS]) + (part[(p4 + 2) * GLA_COLS] + part[(p4 + 3) * GLA_COLS]);
             const int c = col0 + e % GLA_COLS;
             if (c < vdim) out[(size_t)(first + e / GLA_COLS) * out_stride + h * vdim + c] = total;
         }
@@ -151,17 +154,22 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 template <typename T>
 static int launch_scan(const void* q, const void* k, const void* v, int ld, const float* z, int z_stride, const float* z_bias,
                        const int32_t* cu_new, const int32_t* slots, float* state, int n_slots, float* out, int out_stride,
-                       int n_seqs, int H, int dim, int vdim, float q_scale, float inv_tau, cudaStream_t s) {
+                       int n_seqs, int H, int dim, int vdim, float q_scale, float inv_tau, bool single, cudaStream_t s) {
     const dim3 grid((vdim + GLA_COLS - 1) / GLA_COLS, H, n_seqs), block(GLA_THREADS);
     const int rows = (dim + GLA_SPLIT - 1) / GLA_SPLIT;
     cudaError_t e;
 #define GLA_LAUNCH(R)                                                                                                   \
-    e = dl_launch_dependent(gla_scan_kernel<T, R>, grid, block, 0, s, (const T*)q, (const T*)k, (const T*)v, ld,        \
+    if (single)                                                                                                         \
+        e = dl_launch_dependent(gla_scan_kernel<T, R, true>, grid, block, 0, s, (const T*)q, (const T*)k, (const T*)v, ld, \
+                                z, z_stride, z_bias, cu_new, slots, state, n_slots, out, out_stride, H, dim, vdim, \
+                                q_scale, inv_tau);                                                                     \
+    else                                                                                                                \
+    e = dl_launch_dependent(gla_scan_kernel<T, R, false>, grid, block, 0, s, (const T*)q, (const T*)k, (const T*)v, ld,        \
                             z, z_stride, z_bias, cu_new, slots, state, n_slots, out, out_stride, H, dim, vdim, \
                             q_scale, inv_tau)
-    if (rows <= 4) GLA_LAUNCH(4);
-    else if (rows <= 8) GLA_LAUNCH(8);
-    else GLA_LAUNCH(16);
+    if (rows <= 4) { GLA_LAUNCH(4); }
+    else if (rows <= 8) { GLA_LAUNCH(8); }
+    else { GLA_LAUNCH(16); }
 #undef GLA_LAUNCH
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gla_scan: %s", cudaGetErrorString(e));
     return DL_OK;
@@ -170,23 +178,24 @@ static int launch_scan(const void* q, const void* k, const void* v, int ld, cons
 // q, k [tokens, H*dim] and v [tokens, H*vdim]: views with the common row stride ld (columns of one projection);
 // z float32 [tokens, H*dim] (decay logits before the bias), rows z_stride apart; z_bias float32 [H*dim];
 // cu_new int32 [n_seqs + 1] (offsets of each sequence's tokens among the step's rows); slots int32 [n_seqs];
-// state float32 [n_slots, H, dim, vdim], read and updated; out float32 [tokens, H*vdim], rows out_stride apart.
+// state float32 [n_slots, H, dim, vdim], read and updated; out float32 [n_tokens, H*vdim], rows out_stride apart.
 extern "C" int dl_gla_scan(const void* q, const void* k, const void* v, int ld, const float* z, int z_stride,
                            const float* z_bias, int dtype, const int32_t* cu_new, const int32_t* slots, float* state,
-                           int n_slots, float* out, int out_stride, int n_seqs, int H, int dim, int vdim, float q_scale,
-                           float tau, void* stream) {
+                           int n_slots, float* out, int out_stride, int n_seqs, int n_tokens, int H, int dim, int vdim,
+                           float q_scale, float tau, void* stream) {
     DL_REQUIRE(n_seqs >= 0 && H > 0 && dim > 0 && vdim > 0 && n_slots > 0, "gla_scan: bad sizes");
     DL_REQUIRE(dim <= GLA_MAX_DIM, "gla_scan: %d key channels per head, the kernel takes up to %d", dim, GLA_MAX_DIM);
     DL_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
     DL_REQUIRE(out_stride >= H * vdim && z_stride >= H * dim, "gla_scan: rows overlap");
     if (n_seqs == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool single = n_tokens == n_seqs;          // no sequence brings less than one token: each brings exactly one
     if (dtype == DL_F32)
         return launch_scan<float>(q, k, v, ld, z, z_stride, z_bias, cu_new, slots, state, n_slots, out, out_stride, n_seqs, H,
-                                  dim, vdim, q_scale, 1.0f / tau, s);
+                                  dim, vdim, q_scale, 1.0f / tau, single, s);
     if (dtype == DL_BF16)
         return launch_scan<__nv_bfloat16>(q, k, v, ld, z, z_stride, z_bias, cu_new, slots, state, n_slots, out, out_stride,
-                                          n_seqs, H, dim, vdim, q_scale, 1.0f / tau, s);
+                                          n_seqs, H, dim, vdim, q_scale, 1.0f / tau, single, s);
     return dl_fail(DL_ERR_UNSUPPORTED, "gla_scan: dtype %d", dtype);
 }
 

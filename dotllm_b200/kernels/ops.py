@@ -19,7 +19,7 @@ _library.register_signatures({
     "dl_branch_norm_add": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _I, _I, _I, _F, _P],
     "dl_add_rows": [_P, _P, _I, _I, _P],
     "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
-    "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
     "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
@@ -480,7 +480,7 @@ def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_sca
     _int32(slots, "gla slots")
     out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=q.device)
     _library.call("dl_gla_scan", _ptr(q), _ptr(k), _ptr(v), ld, _ptr(z), zs, _ptr(z_bias), _code(q.dtype), _ptr(cu_new),
-                  _ptr(slots), _ptr(state), state.shape[0], _ptr(out), out.stride(0), slots.numel(), n_heads, dim, vdim,
+                  _ptr(slots), _ptr(state), state.shape[0], _ptr(out), out.stride(0), slots.numel(), T, n_heads, dim, vdim,
                   float(q_scale), float(tau), _stream())
     return out
 

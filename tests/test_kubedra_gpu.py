@@ -395,3 +395,28 @@ def test_replay_program_on_a_kubedra_folder(tmp_path, dtype):
     for t in range(10):
         want = [ra[80 + t]] + ([rb[20 + t]] if t % 2 else [])
         assert_rows(read(t + 1), torch.stack(want), tdtype, f"decode step {t}")
+
+
+def test_command_line_makes_and_runs_a_kubedra_folder(tmp_path):
+    """`random` writes a folder from a configuration file, `run` generates from it: greedy tokens are the plain
+    implementation's, a seeded sampled request gives the same tokens twice."""
+    import sys
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(tk.CONFIGS["R"]))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, "-m", "dotllm_b200", "random", str(cfg_path), str(folder), "--seed", "3", "--dtype", "float32"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr[-2000:]
+    cfg, w = tk.read_folder(folder)
+    prompt = tk.random_tokens(11, cfg["vocab"], 9)
+    run = lambda *extra: subprocess.run([sys.executable, "-m", "dotllm_b200", "run", str(folder), "-p", ",".join(map(str, prompt)),
+                                         "-n", "6", "--dtype", "float32", "--json", *extra], cwd=ROOT, capture_output=True, text=True,
+                                        timeout=600)
+    proc = run("-t", "0", "--stop-ids", "")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    tokens = json.loads(proc.stdout)["results"][0]["generated_token_ids"]
+    ref = pk.forward(cfg, w, prompt + tokens)
+    assert tokens == [int(ref[len(prompt) - 1 + i].argmax()) for i in range(6)]
+    a, b = run("-t", "0.9", "--top-k", "30", "-s", "5"), run("-t", "0.9", "--top-k", "30", "-s", "5")
+    assert a.returncode == 0 and json.loads(a.stdout)["results"][0]["generated_token_ids"] == \
+        json.loads(b.stdout)["results"][0]["generated_token_ids"]
