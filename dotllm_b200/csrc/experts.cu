@@ -102,6 +102,14 @@ __device__ __forceinline__ int ex_place(int c, bool vec) {
     constexpr int N = ExVec<T>::N, RUN = 32 * ExVec<T>::N;
     return vec ? (c / RUN) * RUN + (c % N) * 32 + (c % RUN) / N : c;
 }
+// Outputs a block computes for its row: EX_OUT_PER_BLOCK, halved (down to one per warp) while the launch would leave
+// multiprocessors without a block - a decode step has few rows, and each streams whole matrices.
+static inline int ex_outputs_per_block(int rows, int outputs) {
+    int per_block = EX_OUT_PER_BLOCK;
+    while (per_block > EX_WARPS && (long long)rows * ((outputs + per_block - 1) / per_block) < 4 * 148) per_block /= 2;
+    return per_block;
+}
+
 // floats of shared memory that K staged activations take (whole runs when permuted)
 static inline size_t ex_staged(int K, int n_per_lane) { return (size_t)((K + 32 * n_per_lane - 1) / (32 * n_per_lane)) * 32 * n_per_lane; }
 
@@ -122,7 +130,7 @@ __device__ __forceinline__ float ex_row_dot(const T* __restrict__ w, const float
 template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __restrict__ ids, const T* __restrict__ w,
-                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha, int vec) {
+                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha, int vec, int per_block) {
     extern __shared__ float ex_x[];                  // [K]
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -132,8 +140,8 @@ expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __re
     for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[ex_place<T>(c, vec != 0)] = dl_to_f32<T>(xr[c]);
     __syncthreads();
     const int e = ids[r];
-    const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
-    const int n1 = min(ff, n0 + EX_OUT_PER_BLOCK);
+    const int n0 = blockIdx.y * per_block;
+    const int n1 = min(ff, n0 + per_block);
     const bool ok = e >= 0 && e < E;
     const T* we = w + (size_t)(ok ? e : 0) * 2 * ff * K;
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
@@ -152,16 +160,17 @@ extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids
     DL_REQUIRE(ex_staged(K, 8) * sizeof(float) <= 48 * 1024, "expert_gate_up: rows of %d values are more than the kernel takes", K);
     if (tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(tokens * top, (ff + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
+    const int per_block = ex_outputs_per_block(tokens * top, ff);
+    const dim3 grid(tokens * top, (ff + per_block - 1) / per_block), block(32 * EX_WARPS);
     const size_t smem = ex_staged(K, 8) * sizeof(float);
     const int vec = (K % 8 == 0 && ((uintptr_t)w % 16) == 0) ? 1 : 0;      // every weight row starts on a 16-byte boundary
     cudaError_t e;
     if (dtype == DL_F32)
         e = dl_launch_dependent(expert_gate_up_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, ids, (const float*)w,
-                                (float*)out, top, K, ff, E, kind, limit, alpha, vec);
+                                (float*)out, top, K, ff, E, kind, limit, alpha, vec, per_block);
     else if (dtype == DL_BF16)
         e = dl_launch_dependent(expert_gate_up_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride, ids,
-                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha, vec);
+                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha, vec, per_block);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_gate_up: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gate_up: %s", cudaGetErrorString(e));
@@ -174,7 +183,7 @@ template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, const float* __restrict__ weights,
                    const T* __restrict__ w, const float* __restrict__ addend, int addend_stride, float* __restrict__ out,
-                   int top, int ff, int N, int E, int vec) {
+                   int top, int ff, int N, int E, int vec, int per_block) {
     extern __shared__ float ex_h[];                  // [top][ff]
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -187,8 +196,8 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
         ex_h[(size_t)j * staged + ex_place<T>(c - j * ff, vec != 0)] = dl_to_f32<T>(hr[c]);
     }
     __syncthreads();
-    const int n0 = blockIdx.y * EX_OUT_PER_BLOCK;
-    const int n1 = min(N, n0 + EX_OUT_PER_BLOCK);
+    const int n0 = blockIdx.y * per_block;
+    const int n1 = min(N, n0 + per_block);
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
@@ -210,19 +219,20 @@ extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* we
                top, ff);
     if (tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(tokens, (N + EX_OUT_PER_BLOCK - 1) / EX_OUT_PER_BLOCK), block(32 * EX_WARPS);
+    const int per_block = ex_outputs_per_block(tokens, N);
+    const dim3 grid(tokens, (N + per_block - 1) / per_block), block(32 * EX_WARPS);
     const size_t smem = (size_t)top * ex_staged(ff, 8) * sizeof(float);
     const int vec = (ff % 8 == 0 && ((uintptr_t)w % 16) == 0) ? 1 : 0;
     cudaError_t e;
     if (dtype == DL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<float>, grid, block, smem, s, (const float*)h, ids, weights, (const float*)w,
-                                addend, addend_stride, out, top, ff, N, E, vec);
+                                addend, addend_stride, out, top, ff, N, E, vec, per_block);
     } else if (dtype == DL_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(expert_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, ids, weights,
-                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec);
+                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec, per_block);
     } else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_down: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));

@@ -349,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     if (GATED) {
                         float u[32];
                         tc_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
-                        if (GROUPED) {
+                        if (GROUPED || grp.gate_kind != GATE_SILU) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = dl_gate_value(grp.gate_kind, v[i], u[i], grp.limit, grp.alpha);
                         } else {
@@ -460,6 +460,18 @@ extern "C" int dl_gemm_tc_bf16(const void* x, int x_stride, const void* w, void*
     }
     if (out_dtype == DL_F32) return gt_launch<float, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
     return gt_launch<__nv_bfloat16, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+}
+
+// The gated product with another gating than SwiGLU in its epilogue (gating.cuh: the tanh form of gelu, or the clamped
+// sigmoid gating with its limit and alpha).  Arguments as dl_gemm_tc_bf16 with the gated flag; bfloat16 out.
+extern "C" int dl_gemm_tc_gated_bf16(const void* x, int x_stride, const void* w, void* out, int out_stride, int M, int N, int K,
+                                     int gate_kind, float limit, float alpha, int blocks, int* status, void* stream) {
+    DL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && K % 8 == 0, "gemm_tc_gated: M=%d N=%d K=%d (K must be a positive multiple of 8)", M, N, K);
+    DL_REQUIRE(x_stride >= K && x_stride % 8 == 0 && out_stride >= N, "gemm_tc_gated: row strides");
+    DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tc_gated: x and W must be 16-byte aligned");
+    DL_REQUIRE(gate_kind >= 0 && gate_kind <= 2 && status != nullptr, "gemm_tc_gated: unknown gating %d", gate_kind);
+    const GtGroups grp{nullptr, 0, 0, gate_kind, limit, alpha};
+    return gt_launch<__nv_bfloat16, GT_GATED>((cudaStream_t)stream, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp);
 }
 
 // The products of a feed-forward of experts.  x: bf16 [M, K], the rows sorted by expert and every expert's run padded

@@ -13,6 +13,7 @@ from . import library as _library
 _P, _I = _library._P, _library._I
 _library.register_signatures({
     "dl_gemm_tc_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "dl_gemm_tc_gated_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _library._F, _library._F, _I, _P, _P],
     "dl_gemm_tc_qkv_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P],
 })
 
@@ -39,6 +40,17 @@ def run(x, w, out_dtype, fuse_swiglu=False):
     _library.call("dl_gemm_tc_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(),
                   0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K, 1 if fuse_swiglu else 0, BLOCKS,
                   _library.status_word(x.device).data_ptr(), _library.current_stream())
+    return out
+
+
+def run_gated(x, w, gate_kind, limit, alpha):
+    """gating(x Wg^T, x Wu^T) for W = [Wg; Wu] with the gating ``gate_kind`` (``ops.GATINGS``) in the product's epilogue."""
+    M, K = x.shape
+    n_out = w.shape[0] // 2
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    _library.call("dl_gemm_tc_gated_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), n_out, M, n_out, K,
+                  int(gate_kind), float(limit), float(alpha), BLOCKS, _library.status_word(x.device).data_ptr(),
+                  _library.current_stream())
     return out
 
 

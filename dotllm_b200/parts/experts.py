@@ -55,9 +55,10 @@ class RoutedExperts(FeedForward):
             specs[self._expert(e, "gate")] = WeightSpec((self.ff, h))
             specs[self._expert(e, "up")] = WeightSpec((self.ff, h))
             specs[self._expert(e, "down")] = WeightSpec((h, self.ff))
-        specs[self.names["router"]] = WeightSpec((self.n_experts, h), init=("normal", 0.1))
+        # random routers are drawn wide, so that the chosen logits stand clear of the others (few near-ties)
+        specs[self.names["router"]] = WeightSpec((self.n_experts, h), init=("normal", 0.5))
         if self.router_bias:
-            specs[self.names["router_bias"]] = WeightSpec((self.n_experts,), "precise", ("normal", 0.1))
+            specs[self.names["router_bias"]] = WeightSpec((self.n_experts,), "precise", ("normal", 0.5))
         if self.shared_ff:
             for m, shape in (("gate", (self.shared_ff, h)), ("up", (self.shared_ff, h)), ("down", (h, self.shared_ff))):
                 specs[self.names["shared"].format(m=m)] = WeightSpec(shape)
@@ -86,8 +87,7 @@ class RoutedExperts(FeedForward):
         ids, weights = ops.route_topk(x, self.w_router, self.b_router, self.top)
         shared = None
         if self.shared_ff:
-            s = ops.gated_activation(ops.linear(x, self.ws_gate_up, resident=True), self.activation, self.shared_limit,
-                                     self.alpha)
+            s = ops.gated_linear(x, self.ws_gate_up, resident=True, kind=self.activation, limit=self.shared_limit, alpha=self.alpha)
             shared = ops.linear(s, self.ws_down, out_dtype=torch.float32, resident=True)
         if ops.experts_grouped_takes(x, ids, self.w_gate_up, self.w_down):
             # many rows: sorted by expert, both products as tensor-core tiles

@@ -48,10 +48,7 @@ class GatedFeedForward(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, x):
-        if self.activation == "silu":
-            gated = ops.gated_linear(x, self.w_gate_up, resident=True)
-        else:
-            gated = ops.gated_activation(ops.linear(x, self.w_gate_up, resident=True), self.activation, self.limit, self.alpha)
+        gated = ops.gated_linear(x, self.w_gate_up, resident=True, kind=self.activation, limit=self.limit, alpha=self.alpha)
         return ops.linear(gated, self.w_down, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
 

@@ -215,7 +215,9 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     return y.to(out_dtype or x.dtype)
 
 
-def gated_linear(x, w_gate_up, resident=False):
+def gated_linear(x, w_gate_up, resident=False, kind="silu", limit=0.0, alpha=1.0):
+    if kind != "silu":
+        return gated_activation(linear(x, w_gate_up, torch.float32), kind, limit, alpha).to(x.dtype)
     return swiglu(linear(x, w_gate_up, torch.float32)).to(x.dtype)
 
 

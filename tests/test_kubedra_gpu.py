@@ -20,10 +20,10 @@ DTYPES = [torch.float32, torch.bfloat16]
 # A row's rms error over the row's rms.  float32: summation order only, every row is held to the bound.
 # bfloat16: both sides read the same bfloat16 weights; the engine rounds activations to bfloat16 between parts, through
 # up to seven layer runs (seen: median 8e-3, nine rows in ten below 1.3e-2).  A router whose two best logits nearly tie
-# may choose the other expert in bfloat16, which changes that token's row and no other (seen: up to 0.11 in two or three
-# rows of 150); so nine rows in ten are held to HALF the bound, all but 3 % to the bound, and none may exceed LOOSE.
+# may choose the other expert in bfloat16, which changes that token's row and no other (a whole feed-forward branch where
+# one expert is used); so nine rows in ten are held to HALF the bound, all but 3 % to the bound, and none may exceed LOOSE.
 REL = {torch.float32: 3e-5, torch.bfloat16: 4e-2}
-LOOSE = 0.3
+LOOSE = 0.6
 
 
 def row_errors(got, want):
@@ -215,6 +215,23 @@ def test_experts_sorted_into_tensor_core_tiles(T, K, ff, E, top):
     assert torch.allclose(got.cpu().double()[::7], want[::7], rtol=2e-2, atol=2e-2)
     assert torch.allclose(got, rowwise, rtol=1e-2, atol=1e-2)        # both round the gated activations to bfloat16 once
     assert torch.equal(got, ops.experts_grouped(xd, idd, wd_, w_gu, w_d, "clamped_sigmoid", 1.5, 1.702, addend=addend.to(DEV)))
+
+
+@pytest.mark.parametrize("kind,limit,alpha", [("gelu_tanh", 0.0, 1.0), ("clamped_sigmoid", 1.25, 1.702)])
+@pytest.mark.parametrize("T", [5, 40, 300])
+def test_gated_product_with_other_gatings(T, kind, limit, alpha):
+    """The gate/up product with the tanh gelu or the clamped gating: in the tcgen05 product's epilogue for many rows,
+    product then gating kernel for few; both against float64."""
+    x = g64(T, 72, seed=1).to(torch.bfloat16)
+    w = g64(2 * 104, 72, seed=2, scale=0.3).to(torch.bfloat16)
+    got = ops.gated_linear(x.to(DEV), w.to(DEV), resident=True, kind=kind, limit=limit, alpha=alpha)
+    g, u = x.double() @ w[:104].double().T, x.double() @ w[104:].double().T
+    if kind == "gelu_tanh":
+        want = pk.gelu_tanh(g) * u
+    else:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        want = g * torch.sigmoid(alpha * g) * (u + 1)
+    assert got.shape == (T, 104) and torch.allclose(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
