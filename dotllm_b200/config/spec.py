@@ -89,6 +89,8 @@ class ModelSpec:
     # (tensor a part declares, tensor it is the same as): the first is not looked for in a
     # checkpoint, its part is handed the second's tensor (a head tied to the embedding table)
     shared_weights: tuple = ()
+    # tensor names that a checkpoint may hold and no part reads (tolerated, never loaded)
+    optional_weights: tuple = ()
 
     def validate(self) -> None:
         from ..errors import ConfigError

@@ -26,10 +26,17 @@ from ..errors import StepError
 from .step import StepEntry
 
 
+SPARE_PAGES = 64        # pages beyond the stated tokens: every live request may end in a page that is not full
+
+
 class TraceReplayer:
-    def __init__(self, model, max_tokens, out_dir):
+    """``max_tokens`` counts the tokens that live requests hold; the cache hands out whole pages, so it is made
+    `SPARE_PAGES` pages larger than that (room for as many requests' last, partly filled pages)."""
+
+    def __init__(self, model, max_tokens, out_dir, spare_pages=SPARE_PAGES):
+        from ..cache.model_cache import PAGE
         self.model = model
-        self.cache = model.new_cache(max_tokens)
+        self.cache = model.new_cache(int(max_tokens) + int(spare_pages) * PAGE)
         self.out_dir = Path(out_dir)
         self.out_dir.mkdir(parents=True, exist_ok=True)
         self.sequences = {}
@@ -84,7 +91,7 @@ def main(argv=None):
     parser.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
-                        help="most tokens live requests hold at any time (each rounded up to 64)")
+                        help="most tokens live requests hold at any time")
     parser.add_argument("--device", default="cuda")
     args = parser.parse_args(argv)
     from ..model import Model

@@ -49,6 +49,7 @@ class DecoderModel:
             for local, spec in part.weight_specs().items():
                 expected[prefix + local] = spec
             optional |= {prefix + local for local in part.optional_names()}
+        optional |= set(self.spec.optional_weights)
         for name, source in self.spec.shared_weights:
             if name not in expected or source not in expected:
                 raise ValueError(f"shared weight {name!r} = {source!r}: both must be tensors that parts declare")

@@ -51,9 +51,11 @@ def _feed_forward(mlp, prefix):
 
 
 def build_kubedra_spec(cfg: KubedraConfig) -> ModelSpec:
-    layers = []
+    layers, unused = [], []
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
+        if layer.mlp is None:                                  # a checkpoint may still carry the absent sublayer's norms
+            unused += [p + "norm2", p + "norm2b"]
         parts = [LayerPart("mixer_norm", "norm", _norm(cfg, p + "norm1")),
                  LayerPart("mixer", "mixer", _mixer(cfg, layer, p + "mix.")),
                  LayerPart("mixer_post_norm", "norm", _norm(cfg, p + "norm1b"))]
@@ -76,7 +78,8 @@ def build_kubedra_spec(cfg: KubedraConfig) -> ModelSpec:
         head=PartSpec("linear_head", {"vocab_size": cfg.vocab}, "head."),
         stop_token_ids=tuple(cfg.eos_token_id),
         bos_token_id=cfg.bos_token_id,
-        shared_weights=(("head.weight", "embed"),))
+        shared_weights=(("head.weight", "embed"),),
+        optional_weights=tuple(unused))
 
 
 register_architecture("Kubedra", KubedraConfig, build_kubedra_spec, model_types=("kubedra",))

@@ -140,7 +140,7 @@ def test_trace_replay_protocol(cpu_kernels, tmp_path):
              {"step": 2, "entries": [{"id": "a", "tokens": [a[39]], "want": []}], "end": ["a"]},
              {"step": 7, "entries": [{"id": "c", "tokens": b, "want": [8]}], "end": ["c"]}]
     out_dir = tmp_path / "out"
-    replayer = TraceReplayer(Facade(), 128, out_dir)
+    replayer = TraceReplayer(Facade(), 128, out_dir, spare_pages=0)
     printed = io.StringIO()
     replayer.run([json.dumps(s) for s in steps], out=printed)
     assert printed.getvalue().split() == ["done", "0", "done", "1", "done", "2", "done", "7"]

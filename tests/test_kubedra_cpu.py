@@ -19,7 +19,7 @@ CPU = Runtime(torch.float32, torch.device("cpu"))
 
 
 def test_configuration_reads_every_key_and_writes_it_back():
-    for name in ("P", "Q", "R"):
+    for name in ("P", "Q", "R", "S"):
         cfg = config_from_dict(tk.CONFIGS[name])
         assert cfg.to_dict() == tk.CONFIGS[name]
         assert type(cfg).__name__ == "KubedraConfig"
@@ -103,7 +103,7 @@ def load(tmp_path, which):
     return load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder), cfg, weights
 
 
-@pytest.mark.parametrize("which", ["P", "Q", "R"])
+@pytest.mark.parametrize("which", ["P", "Q", "R", "S"])
 def test_steps_cuts_and_batches_agree_with_the_plain_implementation(cpu_kernels, tmp_path, which):
     model, cfg, w = load(tmp_path, which)
     a, b = tk.random_tokens(83, cfg["vocab"], 1), tk.random_tokens(21, cfg["vocab"], 2)

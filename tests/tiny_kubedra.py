@@ -68,6 +68,15 @@ CONFIGS = {
     "R": config(72, 150, 300, 1e-5,
                 [gla(3, 10, 14, 16.0, moe(3, 3, 20, 2.0), rank=3),
                  latent(3, 12, 10, 20, 36, window=5, mlp=dense(50))]),
+    # everything repeats (the run is the whole model and ends in a layer without a feed-forward); a width that is no
+    # multiple of 8; more heads than the decode attention kernel takes on one shared head; an odd latent; a window of one
+    # token and one of exactly a page; a decay of rank 1; every expert but five chosen
+    "S": config(52, 101, 300, 1e-5,
+                [latent(20, 8, 8, 16, 64, window=64, mlp=moe(2, 2, 24, 1.0)),
+                 gla(5, 6, 3, 2.0, dense(30), rank=2),
+                 gla(1, 33, 65, 1.5, moe(9, 4, 16, 0.5, shared=(8, 4.0)), rank=1),
+                 latent(1, 4, 4, 4, 37, window=1, mlp=None)],
+                loop=(0, 4, 2)),
 }
 
 # One mixer alone, for tests that isolate a mechanism.  The latent layer's scores are scaled up until the softmax
