@@ -33,6 +33,7 @@
 // Every wait on an mbarrier is bounded (about a second of clock cycles); on expiry the kernel records
 // a code in `status` and returns after waiting (bounded) for copies in flight.
 #include "common.cuh"
+#include "gating.cuh"
 #include "tma.cuh"
 #include <mutex>
 #include <type_traits>
@@ -105,6 +106,8 @@ struct GsFuse {
     const float* sumsq_in;      // set: output row m is multiplied by rsqrt(sum_p sumsq_in[p * 16 + m] * inv_n + eps)
     int n_parts;
     float inv_n, eps;
+    int gate_kind;              // gated products: 0 = SwiGLU, else a gating of gating.cuh with ...
+    float gate_limit, gate_alpha;   // ... its constants
 };
 
 // acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)} of 8-token group j
@@ -126,8 +129,15 @@ __device__ __forceinline__ void gs_epilogue(const float (&acc_in)[NT][4], TOut* 
             const int col = tile * 8 + g;
             if (col < N) {
                 const float g0 = acc[0], g1 = acc[1];
-                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + col, g0 * (1.0f / (1.0f + expf(-g0))) * acc[2]);
-                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, g1 * (1.0f / (1.0f + expf(-g1))) * acc[3]);
+                if (fuse.gate_kind != GATE_SILU) {
+                    if (tok0 < M)
+                        gs_store<TOut>(out + (size_t)tok0 * out_stride + col, dl_gate_value(fuse.gate_kind, g0, acc[2], fuse.gate_limit, fuse.gate_alpha));
+                    if (tok0 + 1 < M)
+                        gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, dl_gate_value(fuse.gate_kind, g1, acc[3], fuse.gate_limit, fuse.gate_alpha));
+                } else {
+                    if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + col, g0 * (1.0f / (1.0f + expf(-g0))) * acc[2]);
+                    if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, g1 * (1.0f / (1.0f + expf(-g1))) * acc[3]);
+                }
             }
         } else if (std::is_same<TOut, float>::value && fuse.gain != nullptr) {
             float* stream = reinterpret_cast<float*>(out);
@@ -620,6 +630,19 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
                                    int partial_floats, int* counters, int n_counters, int* status, void* stream) {
     return gs_run(x, x_stride, w, out, out_dtype, out_stride, M, N, K, flags, partials, partial_floats, counters, n_counters,
                   status, stream, GsFuse{});
+}
+
+// The gated product with another gating than SwiGLU (gating.cuh) in its epilogue; arguments as dl_gemm_skinny_bf16
+// with the gated flag set.
+extern "C" int dl_gemm_skinny_gated_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
+                                         int out_stride, int M, int N, int K, int flags, int gate_kind, float limit, float alpha,
+                                         float* partials, int partial_floats, int* counters, int n_counters, int* status,
+                                         void* stream) {
+    DL_REQUIRE((flags & 1) == 1 && gate_kind >= 0 && gate_kind <= 2, "gemm_skinny_gated: a gated product with a known gating");
+    GsFuse fuse{};
+    fuse.gate_kind = gate_kind, fuse.gate_limit = limit, fuse.gate_alpha = alpha;
+    return gs_run(x, x_stride, w, out, out_dtype, out_stride, M, N, K, flags, partials, partial_floats, counters, n_counters,
+                  status, stream, fuse);
 }
 
 // The same with the fusions of an add + RMSNorm between two products (either, both or neither):

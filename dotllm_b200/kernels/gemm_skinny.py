@@ -20,6 +20,7 @@ _library.register_signatures({
     "dl_gemm_skinny_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
     "dl_gemm_skinny_fused_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _I, _F, _F,
                                   _P, _I, _P, _I, _P, _P],
+    "dl_gemm_skinny_gated_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P, _I, _P, _P],
     "dl_gemm_skinny_scratch": [_I, _I, _I, _I, _I, _P, _P],
 })
 
@@ -104,6 +105,24 @@ def run(x, w, out_dtype, fuse_swiglu=False, resident=False, row_sums=None, into=
                   sums_out.data_ptr() if sums_out is not None else None,
                   sums_in.data_ptr() if sums_in is not None else None, parts, 1.0 / width, float(eps), *tail)
     return result
+
+
+def takes_gating(x, w):
+    """A gated product with another gating than SwiGLU in its epilogue: the rows of the mma.sync kernel only."""
+    return x.shape[0] <= SKINNY_ROWS and takes(x, w, True)
+
+
+def run_gating(x, w, gate_kind, limit, alpha, resident=False):
+    """gating(x Wg^T, x Wu^T) in x's dtype for W = [Wg; Wu], the gating ``gate_kind`` of ``ops.GATINGS``."""
+    M, K = x.shape
+    n_out = w.shape[0] // 2
+    counters, partials, sms = _device_state(x.device)
+    x_stride = x.stride(0) if M > 1 else max(K, x.stride(0))
+    out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
+    _library.call("dl_gemm_skinny_gated_bf16", x.data_ptr(), x_stride, w.data_ptr(), out.data_ptr(), 1, n_out, M, n_out, K,
+                  1 | (2 if resident else 0), int(gate_kind), float(limit), float(alpha), partials.data_ptr(), partials.numel(),
+                  counters.data_ptr(), counters.numel(), _library.status_word(x.device).data_ptr(), _library.current_stream())
+    return out
 
 
 def scratch_need(M, N, K, fuse_swiglu=False, sms=148):

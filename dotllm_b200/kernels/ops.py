@@ -681,14 +681,18 @@ def gated_linear(x, w_gate_up, resident=False, kind="silu", limit=0.0, alpha=1.0
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] of shape [2I, K]; returns [T, I] in x's dtype.
     In bfloat16 one kernel does the product and the gating in float32: the weight-streaming
     kernel for a few rows, the tcgen05 kernel for many.  In float32 the product is followed by
-    the gating kernel.  ``kind``: another gating of ``GATINGS`` instead of silu; the tcgen05 product
-    has it in its epilogue too (many rows), fewer rows run the product and then ``gated_activation``."""
+    the gating kernel.  ``kind``: another gating of ``GATINGS`` instead of silu; the weight-streaming
+    product (up to 10 rows) and the tcgen05 product (17 rows and more) have it in their epilogues too; the rows
+    between, and float32, run the product and then ``gated_activation``."""
     if kind != "silu":
         x = resolve(x) if isinstance(x, ScaledRows) else x
         _need_cuda(x, w_gate_up)
         if x.dtype == torch.bfloat16 and w_gate_up.dim() == 2 and x.dim() == 2 and x.shape[1] == w_gate_up.shape[1] \
-                and gemm_tc.takes(x, w_gate_up, fuse_swiglu=True):
-            return gemm_tc.run_gated(x, w_gate_up, GATINGS[kind], limit, alpha)
+                and w_gate_up.is_contiguous() and w_gate_up.shape[0] % 2 == 0 and x.shape[0] > 0:
+            if gemm_skinny.takes_gating(x, w_gate_up):
+                return gemm_skinny.run_gating(x, w_gate_up, GATINGS[kind], limit, alpha, resident=resident)
+            if gemm_tc.takes(x, w_gate_up, fuse_swiglu=True):
+                return gemm_tc.run_gated(x, w_gate_up, GATINGS[kind], limit, alpha)
         return gated_activation(linear(x, w_gate_up, resident=resident), kind, limit, alpha)
     if isinstance(x, ScaledRows):
         if w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1] and gemm_skinny.takes(x.data, w_gate_up, True):
