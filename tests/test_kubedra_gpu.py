@@ -262,7 +262,7 @@ def run_cuts(model, tokens, cuts, want_all=True):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("which", ["P", "Q", "R", "S", "T"])
 def test_whole_portions_and_decoding(tmp, which, dtype):
     model, cfg, w, _ = load_pair(tmp, which, dtype)
     tokens = tk.random_tokens(150, cfg["vocab"], 7)
@@ -278,7 +278,7 @@ def test_whole_portions_and_decoding(tmp, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["P", "Q", "S"])
+@pytest.mark.parametrize("which", ["P", "Q", "S", "T"])
 def test_unequal_batches_slots_and_pages_used_again(tmp, which, dtype):
     from dotllm_b200.engine import StepEntry
     model, cfg, w, _ = load_pair(tmp, which, dtype)

@@ -77,6 +77,11 @@ CONFIGS = {
                  gla(1, 33, 65, 1.5, moe(9, 4, 16, 0.5, shared=(8, 4.0)), rank=1),
                  latent(1, 4, 4, 4, 37, window=1, mlp=None)],
                 loop=(0, 4, 2)),
+    # latents of 96 and 32: the widths that the mma.sync prefill attention and the decode kernel take besides 64 and 128
+    "T": config(80, 160, 400, 1e-5,
+                [latent(4, 16, 24, 40, 96, window=100, mlp=dense(64)),
+                 latent(2, 24, 16, 24, 32, mlp=moe(4, 2, 32, 2.0, shared=(16, 2.0))),
+                 gla(2, 32, 32, 8.0, None, rank=8)]),
 }
 
 # One mixer alone, for tests that isolate a mechanism.  The latent layer's scores are scaled up until the softmax
