@@ -25,7 +25,7 @@
 #define GLA_COLS 16
 #define GLA_SPLIT 16
 #define GLA_THREADS (GLA_COLS * GLA_SPLIT)
-#define GLA_MAX_DIM GLA_THREADS          // key channels per head that the scan takes
+#define GLA_MAX_DIM 512                  // key channels per head that the scan takes (GLA_SPLIT threads x 32 rows)
 #define GLA_STAGE 1024                   // values of q (and of k, and of the decays) staged per batch
 #define GLA_MAX_BATCH 16                 // tokens per batch at most
 
@@ -169,7 +169,8 @@ static int launch_scan(const void* q, const void* k, const void* v, int ld, cons
                             q_scale, inv_tau)
     if (rows <= 4) { GLA_LAUNCH(4); }
     else if (rows <= 8) { GLA_LAUNCH(8); }
-    else { GLA_LAUNCH(16); }
+    else if (rows <= 16) { GLA_LAUNCH(16); }
+    else { GLA_LAUNCH(32); }
 #undef GLA_LAUNCH
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gla_scan: %s", cudaGetErrorString(e));
     return DL_OK;

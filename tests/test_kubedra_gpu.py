@@ -72,7 +72,7 @@ def g64(*shape, seed=0, scale=1.0):
 
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,dim,vdim", [(2, 24, 16), (1, 1, 1), (3, 130, 7), (2, 8, 70), (1, 256, 33)])
+@pytest.mark.parametrize("H,dim,vdim", [(2, 24, 16), (1, 1, 1), (3, 130, 7), (2, 8, 70), (1, 256, 33), (1, 300, 20), (1, 512, 5)])
 def test_scan_kernel_alone(H, dim, vdim, dtype):
     """The recurrence over three sequences of unequal lengths in one launch, from states that are not zero, then
     continued token by token from what the first launch left; slots in no particular order."""
