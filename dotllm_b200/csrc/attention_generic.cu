@@ -18,6 +18,10 @@
 // (src/DotLLM.Core/PositionEncoding/IPositionEncoding.cs:10-34): with `softcap` > 0 a score becomes
 // softcap * tanh(score / softcap), and with `slopes` (one float per query head) slope * (key position -
 // query position) is added after that (a penalty that grows with distance).
+//
+// Keys and values may have widths of their own (`hd` key channels, `vd` value channels a head), and the
+// output may be gated per (token, query head): with `gate` (one logit per head in a row of the step's
+// dtype, rows `gate_stride` apart) a head's output is multiplied by sigmoid(logit) as it is written.
 #include "common.cuh"
 
 #define AG_WARPS 4
@@ -28,8 +32,9 @@ __global__ void __launch_bounds__(32 * AG_WARPS)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                          const T* __restrict__ k_pool, const T* __restrict__ v_pool, int n_pages,
                          const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
-                         const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd,
-                         float scale, int window, float softcap, const float* __restrict__ slopes) {
+                         const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd, int vd,
+                         float scale, int window, float softcap, const float* __restrict__ slopes,
+                         const T* __restrict__ gate, int gate_stride) {
     extern __shared__ float q_smem[];                 // [AG_WARPS][hd]
     const int lane = threadIdx.x;
     const int t = blockIdx.x;
@@ -72,28 +77,29 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         const float corr = expf(m - m_new);           // exp(-inf) = 0 on the first tile
         l = l * corr + dl_warp_sum(p);
         m = m_new;
-        const T* vt = v_pool + dl_v_offset(page, nkv, kvh, 0, hd) + in_page0;
+        const T* vt = v_pool + dl_v_offset(page, nkv, kvh, 0, vd) + in_page0;
 #pragma unroll
         for (int i = 0; i < AG_MAX_HD / 32; ++i) {
             const int d = lane + 32 * i;
-            if (i * 32 < hd) {
+            if (i * 32 < vd) {
                 float a = acc[i] * corr;
-                const T* vd = vt + (size_t)(d < hd ? d : 0) * DL_PAGE;
+                const T* vrow = vt + (size_t)(d < vd ? d : 0) * DL_PAGE;
                 for (int kk = 0; kk < 32; ++kk) {
                     const float pk = __shfl_sync(0xffffffffu, p, kk);
                     // masked keys are never read: a reused page may hold anything there
-                    if (j0 + kk >= first && j0 + kk <= pos && d < hd) a += pk * dl_to_f32<T>(vd[kk]);
+                    if (j0 + kk >= first && j0 + kk <= pos && d < vd) a += pk * dl_to_f32<T>(vrow[kk]);
                 }
                 acc[i] = a;
             }
         }
     }
-    const float inv = 1.0f / l;
-    T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
+    float inv = 1.0f / l;
+    if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-dl_to_f32<T>(gate[(size_t)t * gate_stride + h])));
+    T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
-        if (i * 32 < hd && d < hd) orow[d] = dl_from_f32<T>(acc[i] * inv);
+        if (i * 32 < vd && d < vd) orow[d] = dl_from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -115,9 +121,10 @@ __global__ void __launch_bounds__(32 * AG_WARPS)
 attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                                 const T* __restrict__ k_pool, const T* __restrict__ v_pool, int n_pages,
                                 const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
-                                const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd,
-                                float scale, int window, float softcap, const float* __restrict__ slopes) {
-    extern __shared__ float ag_smem[];                // [AG_WARPS][hd] queries, [32][hd + 1] keys, [hd][33] values
+                                const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd, int vd,
+                                float scale, int window, float softcap, const float* __restrict__ slopes,
+                                const T* __restrict__ gate, int gate_stride) {
+    extern __shared__ float ag_smem[];                // [AG_WARPS][hd] queries, [32][hd + 1] keys, [vd][33] values
     const int lane = threadIdx.x, tid = threadIdx.y * 32 + threadIdx.x;
     const int t = blockIdx.x;
     const int h = blockIdx.y * AG_WARPS + threadIdx.y;        // < nh: the host launches this kernel only when nh % AG_WARPS == 0
@@ -146,17 +153,20 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
         __syncthreads();                              // the tile before has been used (and the queries are in place)
         // four values at a time, eight pieces of each tile asked for before the first is stored
         const T* kbase = k_pool + dl_k_offset(page, nkv, kvh, in_page0, hd);
-        const T* vbase = v_pool + dl_v_offset(page, nkv, kvh, 0, hd) + in_page0;
-        const int hd4 = hd / 4, n_vec = 8 * hd;       // pieces of four in a row of K; pieces in a tile (K and V alike)
+        const T* vbase = v_pool + dl_v_offset(page, nkv, kvh, 0, vd) + in_page0;
+        const int hd4 = hd / 4, n_kvec = 8 * hd, n_vvec = 8 * vd;     // pieces of four in a row of K; pieces in a tile of K and of V
+        const int n_vec = max(n_kvec, n_vvec);
         for (int v0 = tid; v0 < n_vec; v0 += 32 * AG_WARPS * 4) {
             float4 kx[4], vx[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const int idx = v0 + b * 32 * AG_WARPS;
                 kx[b] = vx[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (idx < n_vec) {
+                if (idx < n_kvec) {
                     const int key = idx / hd4, c = idx - key * hd4;
                     if (j0 + key >= first && j0 + key <= pos) kx[b] = ag_load4<T>(kbase + (size_t)key * hd + 4 * c);   // masked keys are never read
+                }
+                if (idx < n_vvec) {
                     const int d = idx >> 3, kq = idx & 7;
                     if (j0 + 4 * kq + 3 >= first && j0 + 4 * kq <= pos) vx[b] = ag_load4<T>(vbase + (size_t)d * DL_PAGE + 4 * kq);
                 }
@@ -164,13 +174,15 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const int idx = v0 + b * 32 * AG_WARPS;
-                if (idx < n_vec) {
+                if (idx < n_kvec) {
                     const int key = idx / hd4, c = idx - key * hd4;
                     float* kd = kt + key * (hd + 1) + 4 * c;
                     kd[0] = kx[b].x, kd[1] = kx[b].y, kd[2] = kx[b].z, kd[3] = kx[b].w;
+                }
+                if (idx < n_vvec) {
                     const int d = idx >> 3, kq = idx & 7;
-                    float* vd = vt + d * 33 + 4 * kq;
-                    vd[0] = vx[b].x, vd[1] = vx[b].y, vd[2] = vx[b].z, vd[3] = vx[b].w;
+                    float* vdst = vt + d * 33 + 4 * kq;
+                    vdst[0] = vx[b].x, vdst[1] = vx[b].y, vdst[2] = vx[b].z, vdst[3] = vx[b].w;
                 }
             }
         }
@@ -194,23 +206,24 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
 #pragma unroll
         for (int i = 0; i < AG_MAX_HD / 32; ++i) {
             const int d = lane + 32 * i;
-            if (i * 32 < hd) {
+            if (i * 32 < vd) {
                 float a = acc[i] * corr;
-                const float* vd = vt + (size_t)(d < hd ? d : 0) * 33;
+                const float* vrow = vt + (size_t)(d < vd ? d : 0) * 33;
                 for (int kk = 0; kk < 32; ++kk) {
                     const float pk = __shfl_sync(0xffffffffu, p, kk);
-                    if (j0 + kk >= first && j0 + kk <= pos && d < hd) a += pk * vd[kk];
+                    if (j0 + kk >= first && j0 + kk <= pos && d < vd) a += pk * vrow[kk];
                 }
                 acc[i] = a;
             }
         }
     }
-    const float inv = 1.0f / l;
-    T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
+    float inv = 1.0f / l;
+    if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-dl_to_f32<T>(gate[(size_t)t * gate_stride + h])));
+    T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
-        if (i * 32 < hd && d < hd) orow[d] = dl_from_f32<T>(acc[i] * inv);
+        if (i * 32 < vd && d < vd) orow[d] = dl_from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -218,29 +231,33 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
                                     const void* k_pool, const void* v_pool, int n_pages,
                                     const int32_t* token_seq, const int32_t* token_pos,
                                     const int32_t* block_table, int bt_stride, int n_tokens, int nh, int nkv,
-                                    int hd, float scale, int window, float softcap, const float* slopes, void* stream) {
-    DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0 && n_pages > 0, "attention: bad sizes");
+                                    int hd, int vd, float scale, int window, float softcap, const float* slopes,
+                                    const void* gate, int gate_stride, void* stream) {
+    DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0 && vd > 0 && n_pages > 0, "attention: bad sizes");
+    DL_REQUIRE(vd <= AG_MAX_HD, "attention: value width %d exceeds the supported maximum %d", vd, AG_MAX_HD);
+    DL_REQUIRE(gate == nullptr || gate_stride >= nh, "attention: a row of gate logits holds one per query head");
     DL_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d KV heads", nh, nkv);
     DL_REQUIRE(hd <= AG_MAX_HD, "attention: head_dim %d exceeds the supported maximum %d", hd, AG_MAX_HD);
-    DL_REQUIRE(q_stride >= nh * hd && out_stride >= nh * hd, "attention: row strides shorter than the rows");
+    DL_REQUIRE(q_stride >= nh * hd && out_stride >= nh * vd, "attention: row strides shorter than the rows");
     DL_REQUIRE(window >= 0, "attention: window must be 0 (none) or positive");
     DL_REQUIRE(softcap >= 0.f, "attention: softcap must be 0 (none) or positive");
     if (n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, (nh + AG_WARPS - 1) / AG_WARPS), block(32, AG_WARPS);
     // four heads a block with one KV head between them, and tiles that fit the default shared memory
-    const size_t shared_smem = ((size_t)AG_WARPS * hd + 32 * (hd + 1) + (size_t)hd * 33) * sizeof(float);
+    const size_t shared_smem = ((size_t)AG_WARPS * hd + 32 * (hd + 1) + (size_t)vd * 33) * sizeof(float);
     if (nh % AG_WARPS == 0 && (nh / nkv) % AG_WARPS == 0 && hd % 4 == 0 && shared_smem <= 48 * 1024 &&
         ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0 && (dtype == DL_F32 || dtype == DL_BF16)) {
         if (dtype == DL_F32)
             attention_generic_shared_kernel<float><<<grid, block, shared_smem, s>>>(
                 (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
-                n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, scale, window, softcap, slopes);
+                n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd, scale, window, softcap, slopes,
+                (const float*)gate, gate_stride);
         else
             attention_generic_shared_kernel<__nv_bfloat16><<<grid, block, shared_smem, s>>>(
                 (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-                (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd,
-                scale, window, softcap, slopes);
+                (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd,
+                scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride);
         DL_CHECK_LAUNCH("attention_generic");
         return DL_OK;
     }
@@ -248,12 +265,13 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
     if (dtype == DL_F32)
         attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
-            n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, scale, window, softcap, slopes);
+            n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd, scale, window, softcap, slopes,
+                (const float*)gate, gate_stride);
     else if (dtype == DL_BF16)
         attention_generic_kernel<__nv_bfloat16><<<grid, block, smem, s>>>(
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-            (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd,
-            scale, window, softcap, slopes);
+            (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd,
+            scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "attention: dtype %d", dtype);
     DL_CHECK_LAUNCH("attention_generic");

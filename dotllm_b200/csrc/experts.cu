@@ -1,9 +1,12 @@
 // A feed-forward of many small experts of which every token uses a few.
 //
 //   router:  z = R x + b (float32);  the `top` largest z choose the experts, ties to the lower index;
-//            their weights are the softmax over the chosen z alone
-//   expert:  y = D_e act(G_e x, U_e x)       (act: one of the gatings of gating.cuh)
-//   output:  sum over the chosen experts of weight * y   (+ an addend per token, e.g. a shared expert)
+//            their weights are the softmax over the chosen z alone (scoring 0), or sigmoid(z) of each
+//            chosen expert as it is, not renormalised (scoring 1)
+//   expert:  y = D_e act(G_e x, U_e x)       (act: one of the gatings of gating.cuh), or D_e act(U_e x)
+//            for an activation of one product; the weight multiplies y, or (a row scale) the expert's input x
+//   output:  sum over the chosen experts of weight * y   (+ an addend per token, e.g. a shared expert,
+//            which a per-token logit may gate: addend * sigmoid(logit))
 //
 // Kernels, none of which needs the host to know which experts were chosen (a step can be captured in
 // a graph): the choice (a warp per token, from the float32 logits of the router's product), the gated product (a block per (token, chosen
@@ -20,7 +23,7 @@
 // logits float32 [rows, E] (the router's product), bias float32 [E] or NULL.  A warp per row.
 __global__ void __launch_bounds__(32 * EX_WARPS)
 route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ bias, int32_t* __restrict__ ids,
-                  float* __restrict__ weights, int rows, int E, int top) {
+                  float* __restrict__ weights, int rows, int E, int top, int scoring) {
     extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -52,6 +55,10 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
         __syncwarp();
     }
     if (lane == 0) {
+        if (scoring == 1) {                           // each chosen expert's own sigmoid (monotone in z: the same choice)
+            for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = 1.0f / (1.0f + expf(-chosen[j]));
+            return;
+        }
         const float m = chosen[0];
         float sum = 0.f;
         for (int j = 0; j < top; ++j) sum += expf(chosen[j] - m);
@@ -61,14 +68,15 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
 
 // z float32 [rows, E], rows z_stride apart; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
 extern "C" int dl_route_topk(const float* z, int z_stride, const float* bias, int32_t* ids, float* weights, int rows, int E,
-                             int top, void* stream) {
+                             int top, int scoring, void* stream) {
     DL_REQUIRE(rows >= 0 && E > 0 && top > 0 && top <= E && z_stride >= E, "route_topk: bad sizes E=%d top=%d", E, top);
+    DL_REQUIRE(scoring == 0 || scoring == 1, "route_topk: scoring %d (0: softmax over the chosen, 1: sigmoid)", scoring);
     const size_t smem = (size_t)EX_WARPS * (E + top) * sizeof(float);
     DL_REQUIRE(smem <= 48 * 1024, "route_topk: %d experts are more than the kernel's shared memory takes", E);
     if (rows == 0) return DL_OK;
     const dim3 grid((rows + EX_WARPS - 1) / EX_WARPS), block(32 * EX_WARPS);
     cudaError_t e = dl_launch_dependent(route_topk_kernel, grid, block, smem, (cudaStream_t)stream, z, z_stride, bias, ids, weights,
-                                        rows, E, top);
+                                        rows, E, top, scoring);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "route_topk: %s", cudaGetErrorString(e));
     return DL_OK;
 }
@@ -126,36 +134,41 @@ __device__ __forceinline__ float ex_row_dot(const T* __restrict__ w, const float
 }
 
 // Row r = (token r / top, chosen expert ids[r]):  out[r, n] = act(G_e[n, :] . x[token], U_e[n, :] . x[token]).
-// w: [E, 2 * ff, K], an expert's gate rows first, then its up rows.
+// w: [E, 2 * ff, K], an expert's gate rows first, then its up rows; for an activation of one product w is [E, ff, K]
+// and out[r, n] = act(U_e[n, :] . x[token]).  With `row_scale` (float32 [rows]) the row's input is x[token] * row_scale[r].
 template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __restrict__ ids, const T* __restrict__ w,
-                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha, int vec, int per_block) {
+                      T* __restrict__ out, int top, int K, int ff, int E, int kind, float limit, float alpha, int vec, int per_block,
+                      const float* __restrict__ row_scale) {
     extern __shared__ float ex_x[];                  // [K]
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* xr = x + (size_t)(r / top) * x_stride;
-    for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[ex_place<T>(c, vec != 0)] = dl_to_f32<T>(xr[c]);
+    const float xs = row_scale != nullptr ? row_scale[r] : 1.0f;
+    for (int c = threadIdx.x; c < K; c += blockDim.x) ex_x[ex_place<T>(c, vec != 0)] = dl_to_f32<T>(xr[c]) * xs;
     __syncthreads();
     const int e = ids[r];
     const int n0 = blockIdx.y * per_block;
     const int n1 = min(ff, n0 + per_block);
     const bool ok = e >= 0 && e < E;
-    const T* we = w + (size_t)(ok ? e : 0) * 2 * ff * K;
+    const bool gated = dl_gate_is_gated(kind);
+    const T* we = w + (size_t)(ok ? e : 0) * (gated ? 2 : 1) * ff * K;
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
         const T* gr = we + (size_t)n * K;
-        const T* ur = we + (size_t)(ff + n) * K;
-        const float g = ex_row_dot<T>(gr, ex_x, K, lane, vec != 0);
+        const T* ur = we + (size_t)((gated ? ff : 0) + n) * K;
+        const float g = gated ? ex_row_dot<T>(gr, ex_x, K, lane, vec != 0) : 0.f;
         const float u = ex_row_dot<T>(ur, ex_x, K, lane, vec != 0);
         if (lane == 0) out[(size_t)r * ff + n] = dl_from_f32<T>(ok ? dl_gate_value(kind, g, u, limit, alpha) : 0.f);
     }
 }
 
 extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids, const void* w, void* out, int dtype,
-                                 int tokens, int top, int K, int ff, int E, int kind, float limit, float alpha, void* stream) {
-    DL_REQUIRE(tokens >= 0 && top > 0 && K > 0 && ff > 0 && E > 0 && x_stride >= K && kind >= 0 && kind <= 2,
+                                 int tokens, int top, int K, int ff, int E, int kind, float limit, float alpha,
+                                 const float* row_scale, void* stream) {
+    DL_REQUIRE(tokens >= 0 && top > 0 && K > 0 && ff > 0 && E > 0 && x_stride >= K && kind >= 0 && kind < GATE_KINDS,
                "expert_gate_up: bad arguments");
     DL_REQUIRE(ex_staged(K, 8) * sizeof(float) <= 48 * 1024, "expert_gate_up: rows of %d values are more than the kernel takes", K);
     if (tokens == 0) return DL_OK;
@@ -167,10 +180,10 @@ extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids
     cudaError_t e;
     if (dtype == DL_F32)
         e = dl_launch_dependent(expert_gate_up_kernel<float>, grid, block, smem, s, (const float*)x, x_stride, ids, (const float*)w,
-                                (float*)out, top, K, ff, E, kind, limit, alpha, vec, per_block);
+                                (float*)out, top, K, ff, E, kind, limit, alpha, vec, per_block, row_scale);
     else if (dtype == DL_BF16)
         e = dl_launch_dependent(expert_gate_up_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, x_stride, ids,
-                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha, vec, per_block);
+                                (const __nv_bfloat16*)w, (__nv_bfloat16*)out, top, K, ff, E, kind, limit, alpha, vec, per_block, row_scale);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_gate_up: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gate_up: %s", cudaGetErrorString(e));
@@ -178,12 +191,14 @@ extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids
 }
 
 // out[t, n] = sum_j weights[t, j] * (D_e(t,j)[n, :] . h[t * top + j, :])  (+ addend[t, n]), float32.
-// h: [tokens * top, ff] of dtype; w: [E, N, ff].
+// h: [tokens * top, ff] of dtype; w: [E, N, ff].  weights NULL: every weight is 1.  addend_gate (float32, one logit per
+// token, addend_gate_stride apart) or NULL: the addend is multiplied by sigmoid(logit).
 template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, const float* __restrict__ weights,
                    const T* __restrict__ w, const float* __restrict__ addend, int addend_stride, float* __restrict__ out,
-                   int top, int ff, int N, int E, int vec, int per_block) {
+                   int top, int ff, int N, int E, int vec, int per_block, const float* __restrict__ addend_gate,
+                   int addend_gate_stride) {
     extern __shared__ float ex_h[];                  // [top][ff]
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -198,6 +213,7 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
     __syncthreads();
     const int n0 = blockIdx.y * per_block;
     const int n1 = min(N, n0 + per_block);
+    const float ag = addend_gate != nullptr ? 1.0f / (1.0f + expf(-addend_gate[(size_t)t * addend_gate_stride])) : 1.0f;
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
@@ -205,15 +221,15 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
             if (e < 0 || e >= E) continue;
             const T* wr = w + ((size_t)e * N + n) * ff;
             const float* hj = ex_h + (size_t)j * staged;
-            total += weights[(size_t)t * top + j] * ex_row_dot<T>(wr, hj, ff, lane, vec != 0);
+            total += (weights != nullptr ? weights[(size_t)t * top + j] : 1.0f) * ex_row_dot<T>(wr, hj, ff, lane, vec != 0);
         }
-        if (lane == 0) out[(size_t)t * N + n] = total + (addend != nullptr ? addend[(size_t)t * addend_stride + n] : 0.f);
+        if (lane == 0) out[(size_t)t * N + n] = total + (addend != nullptr ? ag * addend[(size_t)t * addend_stride + n] : 0.f);
     }
 }
 
 extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* weights, const void* w, const float* addend,
                               int addend_stride, float* out, int dtype, int tokens, int top, int ff, int N, int E,
-                              void* stream) {
+                              const float* addend_gate, int addend_gate_stride, void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && N > 0 && E > 0, "expert_down: bad sizes");
     DL_REQUIRE((size_t)top * ex_staged(ff, 8) * sizeof(float) <= 96 * 1024, "expert_down: %d x %d activations are more than the kernel takes",
                top, ff);
@@ -227,12 +243,13 @@ extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* we
     if (dtype == DL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<float>, grid, block, smem, s, (const float*)h, ids, weights, (const float*)w,
-                                addend, addend_stride, out, top, ff, N, E, vec, per_block);
+                                addend, addend_stride, out, top, ff, N, E, vec, per_block, addend_gate, addend_gate_stride);
     } else if (dtype == DL_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(expert_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, ids, weights,
-                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec, per_block);
+                                (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec, per_block, addend_gate,
+                                addend_gate_stride);
     } else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_down: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));
@@ -295,20 +312,44 @@ expert_gather_kernel(const uint4* __restrict__ x, int x_stride16, const int32_t*
     for (int c = threadIdx.x; c < k16; c += blockDim.x) dst[c] = src[c];
 }
 
-// out[t, n] = sum_j weights[t, j] * y[place[t * top + j], n]  (+ addend[t, n]), float32
+// sorted[place[r], :] = x[r / top, :] * row_scale[r], the product taken in float32 and rounded once
+__global__ void __launch_bounds__(256)
+expert_gather_scaled_kernel(const uint4* __restrict__ x, int x_stride16, const int32_t* __restrict__ place, uint4* __restrict__ sorted,
+                            int top, int k16, const float* __restrict__ row_scale) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int r = blockIdx.x;
+    const int p = place[r];
+    if (p < 0) return;
+    const float xs = row_scale[r];
+    const uint4* src = x + (size_t)(r / top) * x_stride16;
+    uint4* dst = sorted + (size_t)p * k16;
+    for (int c = threadIdx.x; c < k16; c += blockDim.x) {
+        uint4 raw = src[c];
+        __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __floats2bfloat162_rn(__low2float(v[i]) * xs, __high2float(v[i]) * xs);
+        dst[c] = raw;
+    }
+}
+
+// out[t, n] = sum_j weights[t, j] * y[place[t * top + j], n]  (+ addend[t, n]), float32; weights NULL: all 1;
+// addend_gate as in the down kernel above
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(const float* __restrict__ y, int y_stride, const int32_t* __restrict__ place, const float* __restrict__ weights,
-                      const float* __restrict__ addend, int addend_stride, float* __restrict__ out, int top, int N) {
+                      const float* __restrict__ addend, int addend_stride, float* __restrict__ out, int top, int N,
+                      const float* __restrict__ addend_gate, int addend_gate_stride) {
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int t = blockIdx.x;
+    const float ag = addend_gate != nullptr ? 1.0f / (1.0f + expf(-addend_gate[(size_t)t * addend_gate_stride])) : 1.0f;
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
             const int p = place[(size_t)t * top + j];
-            if (p >= 0) total += weights[(size_t)t * top + j] * y[(size_t)p * y_stride + n];
+            if (p >= 0) total += (weights != nullptr ? weights[(size_t)t * top + j] : 1.0f) * y[(size_t)p * y_stride + n];
         }
-        out[(size_t)t * N + n] = total + (addend != nullptr ? addend[(size_t)t * addend_stride + n] : 0.f);
+        out[(size_t)t * N + n] = total + (addend != nullptr ? ag * addend[(size_t)t * addend_stride + n] : 0.f);
     }
 }
 
@@ -324,22 +365,28 @@ extern "C" int dl_expert_sort(const int32_t* ids, int rows, int E, int32_t* plac
 }
 
 // x bfloat16 [tokens, K] (rows x_stride apart, 16-byte aligned, K a multiple of 8); sorted bfloat16 [padded rows, K].
-extern "C" int dl_expert_gather(const void* x, int x_stride, const int32_t* place, void* sorted, int rows, int top, int K, void* stream) {
+// row_scale float32 [rows] or NULL: a row is multiplied by its scale on the way.
+extern "C" int dl_expert_gather(const void* x, int x_stride, const int32_t* place, void* sorted, int rows, int top, int K,
+                                const float* row_scale, void* stream) {
     DL_REQUIRE(rows >= 0 && top > 0 && K > 0 && K % 8 == 0 && x_stride % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)sorted % 16) == 0,
                "expert_gather: rows of a multiple of 8 bfloat16 values, 16-byte aligned");
     if (rows == 0) return DL_OK;
-    cudaError_t e = dl_launch_dependent(expert_gather_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x,
-                                        x_stride / 8, place, (uint4*)sorted, top, K / 8);
+    cudaError_t e = row_scale != nullptr
+        ? dl_launch_dependent(expert_gather_scaled_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x,
+                              x_stride / 8, place, (uint4*)sorted, top, K / 8, row_scale)
+        : dl_launch_dependent(expert_gather_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x,
+                              x_stride / 8, place, (uint4*)sorted, top, K / 8);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_gather: %s", cudaGetErrorString(e));
     return DL_OK;
 }
 
 extern "C" int dl_expert_combine(const float* y, int y_stride, const int32_t* place, const float* weights, const float* addend,
-                                 int addend_stride, float* out, int tokens, int top, int N, void* stream) {
+                                 int addend_stride, float* out, int tokens, int top, int N, const float* addend_gate,
+                                 int addend_gate_stride, void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && N > 0 && y_stride >= N, "expert_combine: bad sizes");
     if (tokens == 0) return DL_OK;
     cudaError_t e = dl_launch_dependent(expert_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, y, y_stride, place,
-                                        weights, addend, addend_stride, out, top, N);
+                                        weights, addend, addend_stride, out, top, N, addend_gate, addend_gate_stride);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_combine: %s", cudaGetErrorString(e));
     return DL_OK;
 }

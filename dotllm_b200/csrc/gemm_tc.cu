@@ -357,6 +357,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                             for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
                         }
                     }
+                    if (!GATED && grp.gate_kind == GATE_RELU2) {     // an activation of the one product: relu(v)^2
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f) * fmaxf(v[i], 0.f);
+                    }
                     if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
                 }
             }
@@ -469,8 +473,10 @@ extern "C" int dl_gemm_tc_gated_bf16(const void* x, int x_stride, const void* w,
     DL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && K % 8 == 0, "gemm_tc_gated: M=%d N=%d K=%d (K must be a positive multiple of 8)", M, N, K);
     DL_REQUIRE(x_stride >= K && x_stride % 8 == 0 && out_stride >= N, "gemm_tc_gated: row strides");
     DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tc_gated: x and W must be 16-byte aligned");
-    DL_REQUIRE(gate_kind >= 0 && gate_kind <= 2 && status != nullptr, "gemm_tc_gated: unknown gating %d", gate_kind);
+    DL_REQUIRE(gate_kind >= 0 && gate_kind < GATE_KINDS && status != nullptr, "gemm_tc_gated: unknown gating %d", gate_kind);
     const GtGroups grp{nullptr, 0, 0, gate_kind, limit, alpha};
+    if (!dl_gate_is_gated(gate_kind))            // an activation of one product: w is [N, K], the epilogue applies it
+        return gt_launch<__nv_bfloat16, GT_PLAIN>((cudaStream_t)stream, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp);
     return gt_launch<__nv_bfloat16, GT_GATED>((cudaStream_t)stream, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp);
 }
 
@@ -478,7 +484,8 @@ extern "C" int dl_gemm_tc_gated_bf16(const void* x, int x_stride, const void* w,
 // to whole tiles of 128 rows (M a multiple of 128); tile_expert int32 [M / 128]: the expert of each row tile, -1 for
 // tiles that hold no row.  gated: w is [E, 2N, K] (an expert's N gate rows, then its N up rows) and out bf16 [M, N] =
 // gating(x G_e^T, x U_e^T) with the gating `gate_kind` of gating.cuh; else w is [E, N, K] and out = x W_e^T
-// (float32 or bfloat16).  Rows of padding are computed and written like any other; nobody reads them.
+// (float32 or bfloat16), or, with a `gate_kind` that is an activation of one product, out = act(x W_e^T).
+// Rows of padding are computed and written like any other; nobody reads them.
 extern "C" int dl_gemm_tc_grouped_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype, int out_stride,
                                        int M, int N, int K, int n_experts, const int32_t* tile_expert, int gated, int gate_kind,
                                        float limit, float alpha, int blocks, int* status, void* stream) {
@@ -491,12 +498,12 @@ extern "C" int dl_gemm_tc_grouped_bf16(const void* x, int x_stride, const void* 
     DL_REQUIRE((long long)n_experts * (gated ? 2 : 1) * N < (1ll << 31), "gemm_tc_grouped: too many rows of W");
     cudaStream_t s = (cudaStream_t)stream;
     if (gated) {
-        DL_REQUIRE(out_dtype == DL_BF16 && gate_kind >= 0 && gate_kind <= 2, "gemm_tc_grouped: the gated product writes bfloat16");
+        DL_REQUIRE(out_dtype == DL_BF16 && gate_kind >= 0 && gate_kind < GATE_KINDS && dl_gate_is_gated(gate_kind), "gemm_tc_grouped: the gated product writes bfloat16");
         const GtGroups grp{tile_expert, 2 * N, N, gate_kind, limit, alpha};
         return gt_launch<__nv_bfloat16, GT_GROUPED_GATED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp,
                                                           n_experts);
     }
-    const GtGroups grp{tile_expert, N, 0, 0, 0.f, 0.f};
+    const GtGroups grp{tile_expert, N, 0, dl_gate_is_gated(gate_kind) ? 0 : gate_kind, 0.f, 0.f};
     if (out_dtype == DL_F32)
         return gt_launch<float, GT_GROUPED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp, n_experts);
     return gt_launch<__nv_bfloat16, GT_GROUPED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status, GtQkv{}, grp, n_experts);

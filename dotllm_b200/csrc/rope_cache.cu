@@ -6,6 +6,10 @@
 // V rows into the cache (src/DotLLM.Cuda/CudaKvCache.cs:64-97).  Here the angles come from a
 // float32 cos/sin table built once on the host in float64, the arithmetic is float32, Q is
 // rotated in place and rotated K goes straight to its cache page.  V pages are transposed.
+//
+// Values may have a width of their own (`vd` channels a head against `hd` key channels), and the
+// projections' biases may be added here, in float32, before the rotation (`q_bias` [nh*hd], `k_bias`
+// [nkv*hd], `v_bias` [nkv*vd], each NULL for none): a projection with biases then needs no pass of its own.
 #include "common.cuh"
 
 // The rotation, written with explicit roundings so that both kernels below (and any compiler
@@ -23,7 +27,9 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
                         const float* __restrict__ sin_t, int rotary_dim, int table_rows,
                         const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                         const int32_t* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
-                        T* __restrict__ v_pool, int n_pages, int nh, int nkv, int hd, int write_cache) {
+                        T* __restrict__ v_pool, int n_pages, int nh, int nkv, int hd, int vd,
+                        const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                        const float* __restrict__ v_bias, int write_cache) {
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int t = blockIdx.x;
@@ -35,12 +41,16 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
 
     if ((int)blockIdx.y < nh) {                                   // a query head: rotate in place
         T* p = q + (size_t)t * q_stride + (size_t)blockIdx.y * hd;
+        const float* qb = q_bias != nullptr ? q_bias + (size_t)blockIdx.y * hd : nullptr;
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float x0 = dl_to_f32<T>(p[i]), x1 = dl_to_f32<T>(p[i + half]);
+            float x0 = dl_to_f32<T>(p[i]), x1 = dl_to_f32<T>(p[i + half]);
+            if (qb != nullptr) x0 += qb[i], x1 += qb[i + half];
             const float c = cs[i], s = sn[i];
             p[i] = dl_from_f32<T>(rope_lo(x0, x1, c, s));
             p[i + half] = dl_from_f32<T>(rope_hi(x0, x1, c, s));
         }
+        if (qb != nullptr)                                        // the channels beyond the rotation take their bias too
+            for (int d = 2 * half + threadIdx.x; d < hd; d += blockDim.x) p[d] = dl_from_f32<T>(dl_to_f32<T>(p[d]) + qb[d]);
         return;
     }
     if (!write_cache) return;
@@ -50,21 +60,24 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
     if (page < 0 || page >= n_pages) return;
     const int in_page = pos % DL_PAGE;
     const T* krow = k + (size_t)t * k_stride + (size_t)h * hd;
-    const T* vrow = v + (size_t)t * v_stride + (size_t)h * hd;
+    const T* vrow = v + (size_t)t * v_stride + (size_t)h * vd;
+    const float* kb = k_bias != nullptr ? k_bias + (size_t)h * hd : nullptr;
+    const float* vb = v_bias != nullptr ? v_bias + (size_t)h * vd : nullptr;
     T* kdst = k_pool + dl_k_offset(page, nkv, h, in_page, hd);
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float kv;
         if (d < half) {
-            kv = rope_lo(dl_to_f32<T>(krow[d]), dl_to_f32<T>(krow[d + half]), cs[d], sn[d]);
+            kv = rope_lo(dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f), dl_to_f32<T>(krow[d + half]) + (kb ? kb[d + half] : 0.f), cs[d], sn[d]);
         } else if (d < 2 * half) {
             const int i = d - half;
-            kv = rope_hi(dl_to_f32<T>(krow[i]), dl_to_f32<T>(krow[d]), cs[i], sn[i]);
+            kv = rope_hi(dl_to_f32<T>(krow[i]) + (kb ? kb[i] : 0.f), dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f), cs[i], sn[i]);
         } else {
-            kv = dl_to_f32<T>(krow[d]);
+            kv = dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f);
         }
         kdst[d] = dl_from_f32<T>(kv);
-        v_pool[dl_v_offset(page, nkv, h, d, hd) + in_page] = vrow[d];
     }
+    for (int d = threadIdx.x; d < vd; d += blockDim.x)
+        v_pool[dl_v_offset(page, nkv, h, d, vd) + in_page] = vb ? dl_from_f32<T>(dl_to_f32<T>(vrow[d]) + vb[d]) : vrow[d];
 }
 
 // The same work for steps of many tokens (prefill).  Grid: (tile of 64 packed tokens, head).  A
@@ -82,9 +95,11 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
                              const float* __restrict__ sin_t, int rotary_dim, int table_rows,
                              const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                              const int32_t* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
-                             T* __restrict__ v_pool, int n_pages, int n_tokens, int nh, int nkv, int hd, int write_cache) {
+                             T* __restrict__ v_pool, int n_pages, int n_tokens, int nh, int nkv, int hd, int vd,
+                             const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                             const float* __restrict__ v_bias, int write_cache) {
     extern __shared__ __align__(16) unsigned char rt_raw[];
-    T* tile = reinterpret_cast<T*>(rt_raw);                  // [64 tokens][hd + pad]: V rows of one KV head
+    T* tile = reinterpret_cast<T*>(rt_raw);                  // [64 tokens][vd + pad]: V rows of one KV head
     __shared__ int s_pos[RT_TOKENS], s_page[RT_TOKENS];
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -94,7 +109,7 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
     // KV heads first: their blocks do more (K to its page, V through the transposing tile) and should not start last
     const int kv_first = write_cache ? nkv : 0;
     const bool is_q = (int)blockIdx.y >= kv_first;
-    const int pitch = hd + (int)(4 / sizeof(T));             // an odd number of 32-bit words: no bank conflicts on the transpose
+    const int pitch = vd + (int)(4 / sizeof(T));             // an odd number of 32-bit words (even vd): no bank conflicts on the transpose
     if (threadIdx.x < RT_TOKENS) {
         int pos = -1, page = -1;
         if ((int)threadIdx.x < nt) {
@@ -114,42 +129,60 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
             const int i = idx / half, p = idx - i * half;
             const int pos = s_pos[i];
             if (pos < 0) continue;
-            T* row = q + (size_t)(t0 + i) * q_stride + (size_t)((int)blockIdx.y - kv_first) * hd;
-            const float x0 = dl_to_f32<T>(row[p]), x1 = dl_to_f32<T>(row[p + half]);
+            const int qh = (int)blockIdx.y - kv_first;
+            T* row = q + (size_t)(t0 + i) * q_stride + (size_t)qh * hd;
+            float x0 = dl_to_f32<T>(row[p]), x1 = dl_to_f32<T>(row[p + half]);
+            if (q_bias != nullptr) x0 += q_bias[(size_t)qh * hd + p], x1 += q_bias[(size_t)qh * hd + p + half];
             const float c = cos_t[(size_t)pos * half + p], s = sin_t[(size_t)pos * half + p];
             row[p] = dl_from_f32<T>(rope_lo(x0, x1, c, s));
             row[p + half] = dl_from_f32<T>(rope_hi(x0, x1, c, s));
+        }
+        const int rest = hd - 2 * half;
+        if (q_bias != nullptr && rest > 0) {                 // the channels beyond the rotation take their bias too
+            const int qh = (int)blockIdx.y - kv_first;
+            for (int idx = threadIdx.x; idx < nt * rest; idx += RT_THREADS) {
+                const int i = idx / rest, d = 2 * half + idx - i * rest;
+                if (s_pos[i] < 0) continue;
+                T* row = q + (size_t)(t0 + i) * q_stride + (size_t)qh * hd;
+                row[d] = dl_from_f32<T>(dl_to_f32<T>(row[d]) + q_bias[(size_t)qh * hd + d]);
+            }
         }
         return;
     }
     if (!write_cache) return;
     const int h = blockIdx.y;                                // a KV head: rotate K on its way to the page, stage V
+    const float* kb = k_bias != nullptr ? k_bias + (size_t)h * hd : nullptr;
+    const float* vb = v_bias != nullptr ? v_bias + (size_t)h * vd : nullptr;
+    for (int idx = threadIdx.x; idx < nt * vd; idx += RT_THREADS) {
+        const int i = idx / vd, d = idx - i * vd;
+        const T raw = v[(size_t)(t0 + i) * v_stride + (size_t)h * vd + d];
+        tile[i * pitch + d] = vb ? dl_from_f32<T>(dl_to_f32<T>(raw) + vb[d]) : raw;
+    }
     for (int idx = threadIdx.x; idx < nt * hd; idx += RT_THREADS) {
         const int i = idx / hd, d = idx - i * hd;
         const int page = s_page[i], pos = s_pos[i];
-        tile[i * pitch + d] = v[(size_t)(t0 + i) * v_stride + (size_t)h * hd + d];
         if (page < 0) continue;
         const T* krow = k + (size_t)(t0 + i) * k_stride + (size_t)h * hd;
         const float* cs = cos_t + (size_t)pos * half;
         const float* sn = sin_t + (size_t)pos * half;
         float kv;
         if (d < half) {
-            kv = rope_lo(dl_to_f32<T>(krow[d]), dl_to_f32<T>(krow[d + half]), cs[d], sn[d]);
+            kv = rope_lo(dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f), dl_to_f32<T>(krow[d + half]) + (kb ? kb[d + half] : 0.f), cs[d], sn[d]);
         } else if (d < 2 * half) {
             const int j = d - half;
-            kv = rope_hi(dl_to_f32<T>(krow[j]), dl_to_f32<T>(krow[d]), cs[j], sn[j]);
+            kv = rope_hi(dl_to_f32<T>(krow[j]) + (kb ? kb[j] : 0.f), dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f), cs[j], sn[j]);
         } else {
-            kv = dl_to_f32<T>(krow[d]);
+            kv = dl_to_f32<T>(krow[d]) + (kb ? kb[d] : 0.f);
         }
         k_pool[dl_k_offset(page, nkv, h, pos % DL_PAGE, hd) + d] = dl_from_f32<T>(kv);
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < RT_TOKENS * hd; idx += RT_THREADS) {    // token fastest
+    for (int idx = threadIdx.x; idx < RT_TOKENS * vd; idx += RT_THREADS) {    // token fastest
         const int i = idx % RT_TOKENS, d = idx / RT_TOKENS;
         if (i >= nt) continue;
         const int page = s_page[i];
         if (page < 0) continue;
-        v_pool[dl_v_offset(page, nkv, h, d, hd) + (s_pos[i] % DL_PAGE)] = tile[i * pitch + d];
+        v_pool[dl_v_offset(page, nkv, h, d, vd) + (s_pos[i] % DL_PAGE)] = tile[i * pitch + d];
     }
 }
 
@@ -250,13 +283,13 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
                                    int dtype, const float* cos_t, const float* sin_t, int rotary_dim,
                                    int table_rows, const int32_t* token_seq, const int32_t* token_pos,
                                    const int32_t* block_table, int bt_stride, void* k_pool, void* v_pool,
-                                   int n_pages, int n_tokens, int nh, int nkv, int hd, int write_cache,
-                                   void* stream) {
-    DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "rope_cache_write: bad sizes");
+                                   int n_pages, int n_tokens, int nh, int nkv, int hd, int vd, const float* q_bias,
+                                   const float* k_bias, const float* v_bias, int write_cache, void* stream) {
+    DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0 && vd > 0, "rope_cache_write: bad sizes");
     DL_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
                "rope_cache_write: rotary_dim %d must be even and at most head_dim %d", rotary_dim, hd);
     DL_REQUIRE(rotary_dim == 0 || (cos_t && sin_t && table_rows > 0), "rope_cache_write: rotation needs tables");
-    DL_REQUIRE(q_stride >= nh * hd && (!write_cache || (k_stride >= nkv * hd && v_stride >= nkv * hd)),
+    DL_REQUIRE(q_stride >= nh * hd && (!write_cache || (k_stride >= nkv * hd && v_stride >= nkv * vd)),
                "rope_cache_write: row strides shorter than the rows");
     DL_REQUIRE(!write_cache || (k && v && k_pool && v_pool && block_table && n_pages > 0),
                "rope_cache_write: cache write needs k, v, pools and a block table");
@@ -265,14 +298,15 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
     DL_REQUIRE(nh + nkv <= 65535, "rope_cache_write: too many heads");
     cudaError_t e;
     const size_t elem = dtype == DL_F32 ? 4 : 2;
-    const size_t tile_smem = (size_t)RT_TOKENS * (hd + 4 / elem) * elem;
+    const size_t tile_smem = (size_t)RT_TOKENS * (vd + 4 / elem) * elem;
+    const bool plain = vd == hd && q_bias == nullptr && k_bias == nullptr && v_bias == nullptr;
     if (n_tokens >= RT_TOKENS && tile_smem <= 48 * 1024 && (dtype == DL_F32 || dtype == DL_BF16)) {
         dim3 tgrid((n_tokens + RT_TOKENS - 1) / RT_TOKENS, write_cache ? nh + nkv : nh);
         const bool aligned = ((uintptr_t)q % 16) == 0 && q_stride % 8 == 0 && ((uintptr_t)cos_t % 16) == 0 &&
                              ((uintptr_t)sin_t % 16) == 0 &&
                              (!write_cache || (((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 && k_stride % 8 == 0 &&
                                                v_stride % 8 == 0 && ((uintptr_t)k_pool % 16) == 0));
-        if (dtype == DL_BF16 && rotary_dim == hd && hd % 16 == 0 && aligned) {
+        if (dtype == DL_BF16 && rotary_dim == hd && hd % 16 == 0 && aligned && plain) {
             e = dl_launch_dependent(rope_cache_write_tile_vec_kernel, tgrid, dim3(RT_THREADS), tile_smem, s, (__nv_bfloat16*)q,
                                     q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, cos_t, sin_t,
                                     table_rows, token_seq, token_pos, block_table, bt_stride, (__nv_bfloat16*)k_pool,
@@ -284,13 +318,13 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
             e = dl_launch_dependent(rope_cache_write_tile_kernel<float>, tgrid, dim3(RT_THREADS), tile_smem, s, (float*)q, q_stride,
                                     (const float*)k, k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim, table_rows,
                                     token_seq, token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages,
-                                    n_tokens, nh, nkv, hd, write_cache);
+                                    n_tokens, nh, nkv, hd, vd, q_bias, k_bias, v_bias, write_cache);
         else
             e = dl_launch_dependent(rope_cache_write_tile_kernel<__nv_bfloat16>, tgrid, dim3(RT_THREADS), tile_smem, s,
                                     (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
                                     v_stride, cos_t, sin_t, rotary_dim, table_rows, token_seq, token_pos, block_table,
                                     bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, n_tokens, nh, nkv, hd,
-                                    write_cache);
+                                    vd, q_bias, k_bias, v_bias, write_cache);
         if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "rope_cache_write: %s", cudaGetErrorString(e));
         return DL_OK;
     }
@@ -299,12 +333,13 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
         e = dl_launch_dependent(rope_cache_write_kernel<float>, grid, dim3(128), 0, s, (float*)q, q_stride, (const float*)k,
                                 k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim, table_rows, token_seq,
                                 token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages, nh, nkv, hd,
-                                write_cache);
+                                vd, q_bias, k_bias, v_bias, write_cache);
     else if (dtype == DL_BF16)
         e = dl_launch_dependent(rope_cache_write_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (__nv_bfloat16*)q, q_stride,
                                 (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, cos_t, sin_t,
                                 rotary_dim, table_rows, token_seq, token_pos, block_table, bt_stride,
-                                (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, nh, nkv, hd, write_cache);
+                                (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, nh, nkv, hd, vd, q_bias, k_bias,
+                                v_bias, write_cache);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "rope_cache_write: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "rope_cache_write: %s", cudaGetErrorString(e));

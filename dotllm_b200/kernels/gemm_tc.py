@@ -54,6 +54,16 @@ def run_gated(x, w, gate_kind, limit, alpha):
     return out
 
 
+def run_activated(x, w, kind):
+    """act(x W^T) for W [N, K] and an activation of one product (``ops.UNGATED``) in the product's epilogue."""
+    M, K = x.shape
+    n_out = w.shape[0]
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    _library.call("dl_gemm_tc_gated_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), n_out, M, n_out, K,
+                  int(kind), 0.0, 0.0, BLOCKS, _library.status_word(x.device).data_ptr(), _library.current_stream())
+    return out
+
+
 def takes_qkv(x, w, q_cols, kv_cols, head_dim, rotary_dim, cos, sin, k_pool, v_pool):
     """Can the Q/K/V product of these rows rotate and write the cache in its epilogue?"""
     if not QKV_FUSED or not isinstance(x, torch.Tensor) or x.dim() != 2 or x.shape[0] < QKV_MIN_ROWS:

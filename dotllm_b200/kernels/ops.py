@@ -6,6 +6,8 @@ CPU path.  Parts call these functions through the module (``ops.add_rmsnorm(...)
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from ..errors import KernelError
@@ -21,12 +23,15 @@ _library.register_signatures({
     "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
     "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
-    "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
-    "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
+    "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P],
     "dl_expert_sort": [_P, _I, _I, _P, _P, _I, _P],
-    "dl_expert_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
-    "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P],
+    "dl_expert_gather": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P, _I, _P],
+    "dl_unary_activation": [_P, _I, _P, _I, _I, _I, _I, _P],
+    "dl_softcap": [_P, ctypes.c_longlong, _F, _P],
+    "dl_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
     "dl_gemm_tc_grouped_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _F, _I, _P, _P],
 })
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -277,13 +282,19 @@ def _add_product_scaled(residual, product, gain, eps, out_dtype):
 
 # --------------------------------------------------- position + cache write
 def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table,
-                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True):
+                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True, value_dim=None, biases=None):
     """Rotate Q in place (and K on its way into the cache); store K and V at each token's page.
 
-    q [T, nh*hd], k, v [T, nkv*hd]: row-contiguous views of one dtype.  cos, sin: float32
-    [positions, rotary_dim/2] (None with rotary_dim 0: no rotation).  k_pool [pages, nkv, 64, hd],
-    v_pool [pages, nkv, hd, 64].  block_table int32 [B, P]; token_seq/token_pos int32 [T]."""
-    _need_cuda(q, k, v, cos, sin, token_seq, token_pos, block_table, k_pool, v_pool)
+    q [T, nh*hd], k [T, nkv*hd], v [T, nkv*vd]: row-contiguous views of one dtype (vd = ``value_dim``, default hd).
+    cos, sin: float32 [positions, rotary_dim/2] (None with rotary_dim 0: no rotation).  k_pool [pages, nkv, 64, hd],
+    v_pool [pages, nkv, vd, 64].  block_table int32 [B, P]; token_seq/token_pos int32 [T].  ``biases``: (q, k, v)
+    float32 vectors (each may be None) that the kernel adds to the projections before it rotates them."""
+    vd = int(value_dim or head_dim)
+    qb, kb, vb = biases if biases is not None else (None, None, None)
+    _need_cuda(q, k, v, cos, sin, token_seq, token_pos, block_table, k_pool, v_pool, qb, kb, vb)
+    for b, n, what in ((qb, n_heads * head_dim, "q"), (kb, n_kv_heads * head_dim, "k"), (vb, n_kv_heads * vd, "v")):
+        if b is not None and (b.dtype != torch.float32 or b.shape != (n,) or not b.is_contiguous()):
+            raise KernelError(f"rope: the {what} bias must be contiguous float32 [{n}]")
     T = q.shape[0]
     qs = _rows_view(q, "rope q")
     if q.shape[1] != n_heads * head_dim:
@@ -294,11 +305,11 @@ def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_
     if write_cache:
         ks = _rows_view(k, "rope k")
         vs = _rows_view(v, "rope v")
-        if k.shape != (T, n_kv_heads * head_dim) or v.shape != k.shape:
-            raise KernelError("rope: k and v must be [T, n_kv_heads * head_dim]")
+        if k.shape != (T, n_kv_heads * head_dim) or v.shape != (T, n_kv_heads * vd):
+            raise KernelError("rope: k must be [T, n_kv_heads * head_dim] and v [T, n_kv_heads * value_dim]")
         if k.dtype != q.dtype or v.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
             raise KernelError("rope: q, k, v and the cache must share one dtype")
-        n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim)
+        n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim, vd)
         _int32(block_table, "block_table")
         bt_stride = block_table.shape[1]
         _int32(token_seq, "token_seq")
@@ -316,17 +327,30 @@ def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_
                   int(rotary_dim), table_rows, _ptr(token_seq) if write_cache else None, _ptr(token_pos),
                   _ptr(block_table) if write_cache else None, bt_stride,
                   _ptr(k_pool) if write_cache else None, _ptr(v_pool) if write_cache else None, n_pages,
-                  T, n_heads, n_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+                  T, n_heads, n_kv_heads, head_dim, vd, _ptr(qb), _ptr(kb) if write_cache else None,
+                  _ptr(vb) if write_cache else None, 1 if write_cache else 0, _stream())
 
 
-def _check_pools(k_pool, v_pool, n_kv_heads, head_dim):
+def _check_pools(k_pool, v_pool, n_kv_heads, head_dim, value_dim=None):
+    vd = value_dim or head_dim
     if k_pool.dim() != 4 or not k_pool.is_contiguous() or not v_pool.is_contiguous() \
             or tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim) \
-            or tuple(v_pool.shape) != (k_pool.shape[0], n_kv_heads, head_dim, PAGE):
+            or tuple(v_pool.shape) != (k_pool.shape[0], n_kv_heads, vd, PAGE):
         raise KernelError(f"cache pools must be K [pages, {n_kv_heads}, {PAGE}, {head_dim}] and "
-                          f"V [pages, {n_kv_heads}, {head_dim}, {PAGE}], got {tuple(k_pool.shape)} "
+                          f"V [pages, {n_kv_heads}, {vd}, {PAGE}], got {tuple(k_pool.shape)} "
                           f"and {tuple(v_pool.shape)}")
     return k_pool.shape[0]
+
+
+def head_gate(o, gate, n_heads, width):
+    """o[t, h, :] *= sigmoid(gate[t, h]) in place, for o [T, n_heads*width] and gate [T, n_heads] (a column view is
+    fine) of o's dtype.  Returns o."""
+    _need_cuda(o, gate)
+    if o.dim() != 2 or o.shape[1] != n_heads * width or gate.shape != (o.shape[0], n_heads) or gate.dtype != o.dtype:
+        raise KernelError("head_gate: o [T, heads*width] and one gate logit per (row, head) of o's dtype")
+    _library.call("dl_head_gate", _ptr(o), _rows_view(o, "head_gate o"), _ptr(gate), _rows_view(gate, "head_gate gate"),
+                  _code(o.dtype), o.shape[0], n_heads, width, _stream())
+    return o
 
 
 # ------------------------------------------------------------------ attention
@@ -347,57 +371,67 @@ class ScoreHook:
 
 
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None, score_hook=None):
+              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None):
     """Causal attention of the step's tokens over their sequences' cached keys and values.
 
-    q [T, nh*hd] (row-contiguous view); returns [T, nh*hd] of q's dtype.  ``window`` 0 means
-    every earlier key; w > 0 means the last w keys.  ``plan`` carries the per-step layout
+    q [T, nh*hd] (row-contiguous view); returns [T, nh*vd] of q's dtype (vd = ``value_dim``, default hd).
+    ``window`` 0 means every earlier key; w > 0 means the last w keys.  ``plan`` carries the per-step layout
     (sequence lengths, chunking) that the tensor-core kernels need; without one, for sizes
-    they do not take, or with a ``score_hook``, the generic kernel runs."""
-    _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table)
+    they do not take (values of another width than the keys among them), or with a ``score_hook``, the generic
+    kernel runs.  ``gate`` [T, nh] of q's dtype (a column view is fine): head h's output is multiplied by
+    sigmoid(gate[t, h]) - in the generic kernel's last step, or by ``head_gate`` behind a tensor-core kernel."""
+    vd = int(value_dim or head_dim)
+    _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table, gate)
     T = q.shape[0]
+    gs = 0
+    if gate is not None:
+        gs = _rows_view(gate, "attention gate")
+        if gate.shape != (T, n_heads) or gate.dtype != q.dtype:
+            raise KernelError("attention: the gate holds one logit per (token, head) in q's dtype")
     qs = _rows_view(q, "attention q")
     if q.shape[1] != n_heads * head_dim:
         raise KernelError("attention: q width is not n_heads * head_dim")
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
         raise KernelError("attention: q and the cache must share one dtype")
-    n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim)
+    n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim, vd)
     _int32(token_seq, "token_seq")
     _int32(token_pos, "token_pos")
     _int32(block_table, "block_table")
-    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
     softcap, slopes = 0.0, None
     if score_hook:
         softcap, slopes = score_hook.softcap, score_hook.slopes
         if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (n_heads,) or not slopes.is_contiguous()
                                    or not slopes.is_cuda):
             raise KernelError(f"attention: a score hook's slopes must be contiguous float32 [{n_heads}] on the device")
-    if plan is not None and q.dtype == torch.bfloat16 and not score_hook:
+    if plan is not None and q.dtype == torch.bfloat16 and not score_hook and vd == head_dim:
         if attention_fast.run(q, qs, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
                               n_heads, n_kv_heads, head_dim, float(scale), int(window), plan):
-            return out
+            return out if gate is None else head_gate(out, gate, n_heads, vd)
     _library.call("dl_attention_generic", _ptr(q), qs, _ptr(out), out.stride(0), _code(q.dtype),
                   _ptr(k_pool), _ptr(v_pool), n_pages, _ptr(token_seq), _ptr(token_pos),
-                  _ptr(block_table), block_table.shape[1], T, n_heads, n_kv_heads, head_dim,
-                  float(scale), int(window), float(softcap), _ptr(slopes), _stream())
+                  _ptr(block_table), block_table.shape[1], T, n_heads, n_kv_heads, head_dim, vd,
+                  float(scale), int(window), float(softcap), _ptr(slopes), _ptr(gate), gs, _stream())
     return out
 
 
 def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
-                         n_heads, n_kv_heads, head_dim, scale, window=0, plan=None, score_hook=None):
+                         n_heads, n_kv_heads, head_dim, scale, window=0, plan=None, score_hook=None,
+                         value_dim=None, biases=None, gate=None):
     """``rope_cache_write`` followed by ``attention`` (same arguments, same result).  A bfloat16
     decode step (one new token per sequence) with a full-width rotation of head size 64 or 128, or
     with no rotation, runs as one kernel that rotates q, puts the new keys and values into the
     cache and attends; everything else runs the two kernels one after the other."""
-    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None and not score_hook:
+    plain = biases is None and (value_dim or head_dim) == head_dim
+    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None and not score_hook and plain:
         out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
                                           n_kv_heads, head_dim, float(scale), int(window), plan)
         if out is not None:
-            return out
+            return out if gate is None else head_gate(out, gate, n_heads, head_dim)
     rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
-                     n_heads, n_kv_heads, head_dim, write_cache=k is not None)
+                     n_heads, n_kv_heads, head_dim, write_cache=k is not None, value_dim=value_dim, biases=biases)
     return attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
-                     scale, window, plan=plan, score_hook=score_hook)
+                     scale, window, plan=plan, score_hook=score_hook, value_dim=value_dim, gate=gate)
 
 
 def qkv_rope_cache(x, w_qkv, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
@@ -437,7 +471,8 @@ def swiglu(gate_up):
     return out
 
 
-GATINGS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
+GATINGS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2, "relu2": 3}
+UNGATED = frozenset({"relu2"})      # activations of ONE product, act(u): no gate rows in the matrix (GATE_RELU2 in csrc/gating.cuh)
 
 
 def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
@@ -445,8 +480,8 @@ def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
     (g sigmoid(g) u), "gelu_tanh" (tanh form of gelu(g), times u) or "clamped_sigmoid"
     (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit))."""
     _need_cuda(gate_up)
-    if kind not in GATINGS:
-        raise KernelError(f"gated_activation: unknown gating {kind!r}; known: {sorted(GATINGS)}")
+    if kind not in GATINGS or kind in UNGATED:
+        raise KernelError(f"gated_activation: unknown gating {kind!r}; known: {sorted(set(GATINGS) - UNGATED)}")
     if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
         raise KernelError("gated_activation: need a contiguous [T, 2I] tensor")
     rows, two_i = gate_up.shape
@@ -501,11 +536,23 @@ def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
 
 
 # ---------------------------------------------------------------------- experts
-def route_topk(x, w_router, bias, top):
-    """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and the
-    softmax over the chosen logits alone.  Returns (ids int32 [T, top], weights float32 [T, top])."""
+ROUTER_SCORINGS = {"softmax_chosen": 0, "sigmoid": 1}
+
+
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False):
+    """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and their
+    weights: the softmax over the chosen logits alone (``scoring`` "softmax_chosen"), or each chosen expert's own
+    sigmoid(logit), not renormalised ("sigmoid").  ``experts``: the first that many rows of ``w_router`` are the
+    experts' (default all); rows behind them ride the same product (a per-token gate, say) and only show in the logits.
+    Returns (ids int32 [T, top], weights float32 [T, top]), and the float32 logits [T, rows of w_router] behind them
+    ``with_logits``."""
     _need_cuda(x, w_router, bias)
-    E, K = w_router.shape
+    if scoring not in ROUTER_SCORINGS:
+        raise KernelError(f"route_topk: unknown scoring {scoring!r}; known: {sorted(ROUTER_SCORINGS)}")
+    rows_w, K = w_router.shape
+    E = int(experts) if experts is not None else rows_w
+    if not 0 < E <= rows_w:
+        raise KernelError(f"route_topk: {E} experts in a matrix of {rows_w} rows")
     if x.shape[1] != K or x.dtype != w_router.dtype or not w_router.is_contiguous():
         raise KernelError(f"route_topk: x {tuple(x.shape)} does not match the router {tuple(w_router.shape)}")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape != (E,) or not bias.is_contiguous()):
@@ -516,46 +563,69 @@ def route_topk(x, w_router, bias, top):
     z = linear(x, w_router, out_dtype=torch.float32, resident=True)         # float32 accumulation, float32 logits
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    _library.call("dl_route_topk", _ptr(z), z.stride(0) if T > 1 else E, _ptr(bias), _ptr(ids), _ptr(weights), T, E, top, _stream())
-    return ids, weights
+    _library.call("dl_route_topk", _ptr(z), z.stride(0) if T > 1 else rows_w, _ptr(bias), _ptr(ids), _ptr(weights), T, E, top,
+                  ROUTER_SCORINGS[scoring], _stream())
+    return (ids, weights, z) if with_logits else (ids, weights)
 
 
-def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0):
+def _row_scale(row_scale, ids, what):
+    if row_scale is not None and (row_scale.dtype != torch.float32 or row_scale.shape != ids.shape or not row_scale.is_contiguous()):
+        raise KernelError(f"{what}: the row scale must be contiguous float32 [T, top]")
+    return row_scale
+
+
+def _addend(addend, addend_gate, T, N, what):
+    """(row stride of the addend, row stride of its gate) after checking both."""
+    astride = gstride = 0
+    if addend is not None:
+        astride = _rows_view(addend, what + " addend")
+        if addend.dtype != torch.float32 or addend.shape != (T, N):
+            raise KernelError(f"{what}: the addend must be float32 [T, N]")
+    if addend_gate is not None:
+        if addend is None or addend_gate.dtype != torch.float32 or addend_gate.dim() != 2 or addend_gate.shape[0] != T \
+                or addend_gate.stride(1) != 1:
+            raise KernelError(f"{what}: the addend's gate is one float32 logit per token (column 0 of a [T, n] view)")
+        gstride = addend_gate.stride(0) if T > 1 else max(addend_gate.stride(0), 1)
+    return astride, gstride
+
+
+def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0, row_scale=None):
     """Row (t, j) = act(G_e x_t, U_e x_t) for e = ids[t, j].  x [T, K]; w_gate_up [E, 2*ff, K] (an expert's gate
-    rows, then its up rows); returns [T*top, ff] in x's dtype."""
-    _need_cuda(x, ids, w_gate_up)
+    rows, then its up rows); returns [T*top, ff] in x's dtype.  For an activation of one product (``UNGATED``) the
+    matrices are [E, ff, K] and the row is act(U_e x_t).  ``row_scale`` float32 [T, top]: row (t, j) takes
+    x_t * row_scale[t, j] as its input (an expert whose weight multiplies what goes in, not what comes out)."""
+    _need_cuda(x, ids, w_gate_up, row_scale)
     xs = _rows_view(x, "expert x")
     _int32(ids, "expert ids")
-    if w_gate_up.dim() != 3 or not w_gate_up.is_contiguous() or w_gate_up.shape[1] % 2 or w_gate_up.shape[2] != x.shape[1] \
+    halves = 1 if kind in UNGATED else 2
+    if w_gate_up.dim() != 3 or not w_gate_up.is_contiguous() or w_gate_up.shape[1] % halves or w_gate_up.shape[2] != x.shape[1] \
             or w_gate_up.dtype != x.dtype or ids.dim() != 2 or ids.shape[0] != x.shape[0]:
-        raise KernelError("expert_gate_up: x [T, K], ids [T, top], weights [E, 2*ff, K] of x's dtype")
-    E, two_ff, K = w_gate_up.shape
+        raise KernelError("expert_gate_up: x [T, K], ids [T, top], weights [E, 2*ff, K] ([E, ff, K] without a gate) of x's dtype")
+    E, rows_w, K = w_gate_up.shape
+    ff = rows_w // halves
     T, top = ids.shape
-    out = torch.empty((T * top, two_ff // 2), dtype=x.dtype, device=x.device)
+    out = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
     _library.call("dl_expert_gate_up", _ptr(x), xs, _ptr(ids), _ptr(w_gate_up), _ptr(out), _code(x.dtype), T, top, K,
-                  two_ff // 2, E, GATINGS[kind], float(limit), float(alpha), _stream())
+                  ff, E, GATINGS[kind], float(limit), float(alpha), _ptr(_row_scale(row_scale, ids, "expert_gate_up")), _stream())
     return out
 
 
-def expert_down(h, ids, weights, w_down, addend=None):
+def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None):
     """out[t] = sum_j weights[t, j] * D_e(t,j) h[t*top + j]  (+ addend[t]), float32 [T, N].  h [T*top, ff];
-    w_down [E, N, ff] of h's dtype; addend float32 [T, N] (rows contiguous) or None."""
-    _need_cuda(h, ids, weights, w_down, addend)
+    w_down [E, N, ff] of h's dtype; weights float32 [T, top] or None (all 1); addend float32 [T, N] (rows contiguous)
+    or None; ``addend_gate`` float32, one logit per token (column 0 of a [T, n] view): the addend times its sigmoid."""
+    _need_cuda(h, ids, weights, w_down, addend, addend_gate)
     _int32(ids, "expert ids")
     T, top = ids.shape
     if w_down.dim() != 3 or not w_down.is_contiguous() or w_down.dtype != h.dtype or not h.is_contiguous() \
-            or h.shape != (T * top, w_down.shape[2]) or weights.dtype != torch.float32 or weights.shape != ids.shape \
-            or not weights.is_contiguous():
+            or h.shape != (T * top, w_down.shape[2]) or (weights is not None and (
+                weights.dtype != torch.float32 or weights.shape != ids.shape or not weights.is_contiguous())):
         raise KernelError("expert_down: h [T*top, ff], ids and float32 weights [T, top], matrices [E, N, ff] of h's dtype")
     E, N, ff = w_down.shape
-    astride = 0
-    if addend is not None:
-        astride = _rows_view(addend, "expert addend")
-        if addend.dtype != torch.float32 or addend.shape != (T, N):
-            raise KernelError("expert_down: the addend must be float32 [T, N]")
+    astride, gstride = _addend(addend, addend_gate, T, N, "expert_down")
     out = torch.empty((T, N), dtype=torch.float32, device=h.device)
     _library.call("dl_expert_down", _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_down), _ptr(addend), astride, _ptr(out),
-                  _code(h.dtype), T, top, ff, N, E, _stream())
+                  _code(h.dtype), T, top, ff, N, E, _ptr(addend_gate), gstride, _stream())
     return out
 
 
@@ -573,16 +643,20 @@ def experts_grouped_takes(x, ids, w_gate_up, w_down):
             and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
 
 
-def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1.0, addend=None):
+def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1.0, addend=None, row_scale=None,
+                    addend_gate=None):
     """The same result as ``expert_gate_up`` followed by ``expert_down``, for many rows: the (token, choice) rows are
     sorted by expert on the device, each expert's run padded to whole tiles, and the two products run on the tensor
     cores (tcgen05) with the gating in the first one's epilogue; a last kernel sums every token's choices with
-    their weights (and the addend).  Shapes depend only on the step's sizes, never on the choice."""
-    _need_cuda(x, ids, weights, w_gate_up, w_down, addend)
+    their weights (and the addend).  Shapes depend only on the step's sizes, never on the choice.  ``weights`` None,
+    ``row_scale``, ``addend_gate`` and activations of one product as in those two (the row scale is applied as the rows
+    are gathered, the activation in the first product's epilogue)."""
+    _need_cuda(x, ids, weights, w_gate_up, w_down, addend, row_scale, addend_gate)
     _int32(ids, "expert ids")
     T, top = ids.shape
-    E, two_ff, K = w_gate_up.shape
-    ff, N = two_ff // 2, w_down.shape[1]
+    gated = kind not in UNGATED
+    E, rows_w, K = w_gate_up.shape
+    ff, N = (rows_w // 2 if gated else rows_w), w_down.shape[1]
     rows = T * top
     tiles = (rows + EXPERT_TILE - 1) // EXPERT_TILE + E - 1          # every expert may end in a tile that is not full
     dev = x.device
@@ -590,21 +664,19 @@ def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1
     tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
     _library.call("dl_expert_sort", _ptr(ids), rows, E, _ptr(place), _ptr(tile_expert), tiles, _stream())
     sorted_x = torch.empty((tiles * EXPERT_TILE, K), dtype=torch.bfloat16, device=dev)
-    _library.call("dl_expert_gather", _ptr(x), x.stride(0) if T > 1 else K, _ptr(place), _ptr(sorted_x), rows, top, K, _stream())
+    _library.call("dl_expert_gather", _ptr(x), x.stride(0) if T > 1 else K, _ptr(place), _ptr(sorted_x), rows, top, K,
+                  _ptr(_row_scale(row_scale, ids, "experts_grouped")), _stream())
     status = _library.status_word(dev).data_ptr()
     h = torch.empty((tiles * EXPERT_TILE, ff), dtype=torch.bfloat16, device=dev)
     _library.call("dl_gemm_tc_grouped_bf16", _ptr(sorted_x), K, _ptr(w_gate_up), _ptr(h), 1, ff, tiles * EXPERT_TILE, ff, K, E,
-                  _ptr(tile_expert), 1, GATINGS[kind], float(limit), float(alpha), 0, status, _stream())
+                  _ptr(tile_expert), 1 if gated else 0, GATINGS[kind], float(limit), float(alpha), 0, status, _stream())
     y = torch.empty((tiles * EXPERT_TILE, N), dtype=torch.float32, device=dev)
     _library.call("dl_gemm_tc_grouped_bf16", _ptr(h), ff, _ptr(w_down), _ptr(y), 0, N, tiles * EXPERT_TILE, N, ff, E,
                   _ptr(tile_expert), 0, 0, 0.0, 0.0, 0, status, _stream())
-    astride = 0
-    if addend is not None:
-        astride = _rows_view(addend, "expert addend")
-        if addend.dtype != torch.float32 or addend.shape != (T, N):
-            raise KernelError("experts_grouped: the addend must be float32 [T, N]")
+    astride, gstride = _addend(addend, addend_gate, T, N, "experts_grouped")
     out = torch.empty((T, N), dtype=torch.float32, device=dev)
-    _library.call("dl_expert_combine", _ptr(y), N, _ptr(place), _ptr(weights), _ptr(addend), astride, _ptr(out), T, top, N, _stream())
+    _library.call("dl_expert_combine", _ptr(y), N, _ptr(place), _ptr(weights), _ptr(addend), astride, _ptr(out), T, top, N,
+                  _ptr(addend_gate), gstride, _stream())
     return out
 
 
@@ -675,6 +747,38 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def unary_activation(x, kind):
+    """act(x) for an activation of one product (``UNGATED``); x [T, N] (rows contiguous), returns a contiguous [T, N]."""
+    _need_cuda(x)
+    if kind not in UNGATED:
+        raise KernelError(f"unary_activation: {kind!r} is no activation of one product; known: {sorted(UNGATED)}")
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _library.call("dl_unary_activation", _ptr(x), _rows_view(x, "unary_activation x"), _ptr(out), _code(x.dtype), x.shape[0],
+                  x.shape[1], GATINGS[kind], _stream())
+    return out
+
+
+def activated_linear(x, w, kind, resident=False):
+    """act(x W^T) for W [N, K] and an activation of one product (``UNGATED``); returns [T, N] in x's dtype.  Many bfloat16
+    rows: the tcgen05 product with the activation in its epilogue; otherwise the product and then the activation."""
+    x = resolve(x) if isinstance(x, ScaledRows) else x
+    _need_cuda(x, w)
+    if kind not in UNGATED:
+        raise KernelError(f"activated_linear: {kind!r} is no activation of one product; known: {sorted(UNGATED)}")
+    if x.dtype == torch.bfloat16 and w.dim() == 2 and x.dim() == 2 and x.shape[1] == w.shape[1] and gemm_tc.takes(x, w):
+        return gemm_tc.run_activated(x, w, GATINGS[kind])
+    return unary_activation(linear(x, w, resident=resident), kind)
+
+
+def softcap(values, cap):
+    """values = cap * tanh(values / cap) in place (float32, contiguous); returns values."""
+    _need_cuda(values)
+    if values.dtype != torch.float32 or not values.is_contiguous() or not cap > 0:
+        raise KernelError("softcap: contiguous float32 values and a positive cap")
+    _library.call("dl_softcap", _ptr(values), values.numel(), float(cap), _stream())
+    return values
 
 
 def gated_linear(x, w_gate_up, resident=False, kind="silu", limit=0.0, alpha=1.0):

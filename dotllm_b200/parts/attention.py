@@ -6,6 +6,13 @@ encoding of Q and K, cache write, attention of the new queries over everything c
 projection.  scale = 1/sqrt(head_dim) and query head h reads KV head h // (n_heads/n_kv_heads)
 (src/DotLLM.Cpu/Kernels/Attention.cs:47,76,106).  The three projections are stacked into one
 matrix when the weights are bound, so one product yields q, k and v side by side.
+
+Options beyond the reference's block, each a parameter: values of another width than the keys (``value_dim``),
+biases on the three projections (added in float32 by the kernel that rotates and writes the cache), a gate per
+(token, query head) from a projection of the mixer's input (``gate`` "head_sigmoid": the head's output times
+sigmoid of its logit, before the output projection; the gate's rows ride the stacked product), and an execution
+that reads another execution's keys and values (the schedule's ``cache_of``: such a layer has no key and value
+projections, ``own_kv`` False).
 """
 from __future__ import annotations
 
@@ -26,7 +33,15 @@ class AttentionMixer(Mixer):
     """params: ``n_heads``, ``n_kv_heads``, ``head_dim``, ``window`` (None = all keys),
     ``position`` ({"kind", "params"} of a position encoding), optional ``scale``, optional ``score``
     ({"softcap": c, "slopes": [one per head]}: scores are capped and biased by distance before the
-    softmax, which sends the mixer to the generic attention kernel)."""
+    softmax, which sends the mixer to the generic attention kernel); optional ``value_dim`` (per head, default
+    ``head_dim``), ``bias`` (True: q, k and v have biases), ``gate`` (None or "head_sigmoid"), ``own_kv`` (False: no key
+    and value projections, the layer reads another's cache) and ``tensors``: the local names of ``q``, ``k``, ``v``,
+    ``o``, ``gate`` and the bias suffix ``bias`` (appended to a projection's name)."""
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "gate": "g_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
+    GATES = (None, "head_sigmoid")
+    ROW_STEP = 16                # the stacked matrix's rows are a multiple of this: its product's rows stay 16-byte aligned
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
@@ -48,35 +63,102 @@ class AttentionMixer(Mixer):
         self.score_hook = ops.ScoreHook(score.get("softcap", 0.0),
                                         None if slopes is None else torch.tensor(list(slopes), dtype=torch.float32,
                                                                                  device=runtime.device))
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
+        self.bias = bool(params.get("bias", False))
+        self.gate = params.get("gate")
+        if self.gate not in self.GATES:
+            raise ConfigError(f"attention: unknown gate {self.gate!r}; known: {list(self.GATES)}")
+        self.own_kv = bool(params.get("own_kv", True))
+        self.names = dict(self.NAMES, **(params.get("tensors") or {}))
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv_heads * self.head_dim
+        self.v_width = self.n_kv_heads * self.value_dim
+        self.o_dim = self.n_heads * self.value_dim
+        # the reference's block as it is (one matrix of q, k and v rows, nothing added): its fused paths apply
+        self.plain = not self.bias and self.gate is None and self.value_dim == self.head_dim and self.own_kv
         self.w_qkv = None
         self.w_o = None
+        self.biases = None
 
     def weight_specs(self):
-        h = self.hidden_size
-        return {"q_proj.weight": WeightSpec((self.q_dim, h)),
-                "k_proj.weight": WeightSpec((self.kv_dim, h)),
-                "v_proj.weight": WeightSpec((self.kv_dim, h)),
-                "o_proj.weight": WeightSpec((h, self.q_dim))}
+        h, n = self.hidden_size, self.names
+        specs = {n["q"]: WeightSpec((self.q_dim, h))}
+        if self.own_kv:
+            specs[n["k"]] = WeightSpec((self.kv_dim, h))
+            specs[n["v"]] = WeightSpec((self.v_width, h))
+        if self.bias:
+            specs[n["q_bias"]] = WeightSpec((self.q_dim,), "precise", ("normal", 0.1))
+            if self.own_kv:
+                specs[n["k_bias"]] = WeightSpec((self.kv_dim,), "precise", ("normal", 0.1))
+                specs[n["v_bias"]] = WeightSpec((self.v_width,), "precise", ("normal", 0.1))
+        if self.gate:
+            specs[n["gate"]] = WeightSpec((self.n_heads, h), init=("normal", 0.1))
+        specs[n["o"]] = WeightSpec((h, self.o_dim))
+        return specs
 
     def bind(self, tensors):
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
-                                tensors["v_proj.weight"]], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        n = self.names
+        rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
+        if self.gate:
+            rows.append(tensors[n["gate"]])
+        if not self.plain:
+            total = sum(r.shape[0] for r in rows)
+            pad = -total % self.ROW_STEP
+            if pad:
+                rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        if self.bias:
+            self.biases = (tensors[n["q_bias"]].contiguous(),
+                           tensors[n["k_bias"]].contiguous() if self.own_kv else None,
+                           tensors[n["v_bias"]].contiguous() if self.own_kv else None)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
 
     def cache_need(self):
-        return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, window=self.window)
+        return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, window=self.window,
+                         v_dim=self.value_dim if self.value_dim != self.head_dim else None)
 
     takes_scaled_rows = True                    # x goes straight into the Q/K/V product
 
+    def _forward_general(self, x, step, cache_view):
+        """With biases, a gate, values of their own width or another layer's cache: one stacked product (q, then k and v
+        where the layer has its own, then the gate's logits), one kernel that adds the biases, rotates and writes the
+        cache, attention (gated in its last step, or by a kernel behind the tensor-core ones), the output projection."""
+        if cache_view.writes != self.own_kv:
+            raise ConfigError("attention: a layer without key and value projections must read another layer's cache "
+                              "(and one with them keeps its own)")
+        qd, kvd, vw = self.q_dim, self.kv_dim, self.v_width
+        y = ops.linear(x, self.w_qkv, resident=True)
+        q, at = y[:, :qd], qd
+        k = v = None
+        if self.own_kv:
+            k, v, at = y[:, at:at + kvd], y[:, at + kvd:at + kvd + vw], at + kvd + vw
+        g = y[:, at:at + self.n_heads] if self.gate else None
+        fused = self.position.fused_rotary()
+        if fused is None:
+            if self.biases is not None:
+                raise ConfigError("attention: biases need a position encoding that rides the cache-write kernel")
+            self.position.apply(q, k, step.token_pos)
+            cos = sin = None
+            rotary_dim = 0
+        else:
+            cos, sin, rotary_dim = fused
+        a = ops.rope_cache_attention(q, k, v, cos, sin, rotary_dim, step.token_seq, step.token_pos,
+                                     cache_view.block_table, cache_view.k, cache_view.v,
+                                     self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                     int(self.window or 0), plan=step.attention_plan,
+                                     score_hook=self.score_hook if self.score_hook else None,
+                                     value_dim=self.value_dim, biases=self.biases, gate=g)
+        return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
+
     def forward(self, x, step, cache_view):
+        if not self.plain:
+            return self._forward_general(x, step, cache_view)
         qd, kvd = self.q_dim, self.kv_dim
         fused = self.position.fused_rotary()
-        if cache_view.writes and fused is not None:
+        if cache_view.writes and fused is not None and fused[2]:
             # a prompt step: rotation and cache write in the product's epilogue, then attention over the cache
             q = ops.qkv_rope_cache(x, self.w_qkv, fused[0], fused[1], fused[2], step.token_seq, step.token_pos,
                                    cache_view.block_table, cache_view.k, cache_view.v, self.n_heads, self.n_kv_heads,

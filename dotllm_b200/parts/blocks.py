@@ -12,7 +12,8 @@ from .base import Arrangement, normalised_for, register_arrangement
 
 
 class PreNormBlock(Arrangement):
-    needs = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+    """The feed-forward and its norm may be absent (a layer that only mixes): the mixer's branch is handed on."""
+    needs = ("mixer_norm", "mixer")
     narrows = True
 
     def forward(self, residual, pending, step, cache_view, keep_rows=None):
@@ -24,6 +25,8 @@ class PreNormBlock(Arrangement):
             from ..kernels import ops
             residual = ops.gather_rows(residual, keep_rows)
             a = ops.narrow_rows(a, keep_rows)
+        if "feed_forward" not in self.parts:
+            return residual, a
         n = normalised_for(self.feed_forward, self.feed_forward_norm, residual, a)
         return residual, self.feed_forward.forward(n)
 

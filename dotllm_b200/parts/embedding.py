@@ -14,18 +14,20 @@ from .base import Part, WeightSpec, register_embedding, register_head
 
 
 class TokenEmbedding(Part):
-    """params: ``vocab_size``."""
+    """params: ``vocab_size``; optional ``tensor`` (the table's local name, default "weight") and ``init_std``."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.vocab_size = int(params["vocab_size"])
+        self.tensor_name = str(params.get("tensor", "weight"))
         self.table = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor_name: WeightSpec((self.vocab_size, self.hidden_size),
+                                             init=("normal", float(self.params.get("init_std", 0.02))))}
 
     def bind(self, tensors):
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.tensor_name].contiguous()
 
     def forward(self, step):
         """The step's tokens (``step.tokens`` int32 [T]) -> float32 [T, H]: the start of the residual
@@ -61,19 +63,23 @@ class TokenPositionEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: ``vocab_size``.  Whether its matrix is the embedding table is the model description's
-    business (``ModelSpec.shared_weights``): the part is handed a [vocab, hidden] matrix either way."""
+    """params: ``vocab_size``; optional ``softcap`` (c > 0: logits become c tanh(logits / c)) and ``tensor`` (the
+    local name of the matrix, default "weight"; "" when the prefix is the whole name).  Whether its matrix is the
+    embedding table is the model description's business (``ModelSpec.shared_weights``): the part is handed a
+    [vocab, hidden] matrix either way."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.vocab_size = int(params["vocab_size"])
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.tensor_name = str(params.get("tensor", "weight"))
         self.weight = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor_name: WeightSpec((self.vocab_size, self.hidden_size))}
 
     def bind(self, tensors):
-        w = tensors["weight"]
+        w = tensors[self.tensor_name]
         self.weight = w if w.is_contiguous() else w.contiguous()
 
     def weight_bytes(self):
@@ -83,7 +89,8 @@ class LinearHead(Part):
 
     def forward(self, x):
         """[R, H] in the run dtype -> float32 logits [R, vocab]."""
-        return ops.linear(x, self.weight, out_dtype=torch.float32, resident=True)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32, resident=True)
+        return ops.softcap(logits, self.softcap) if self.softcap > 0 else logits
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -6,7 +6,11 @@ Frequencies f_i = theta^(-2i/d), angle = pos * f_i, cos/sin tabulated per positi
 scaling keys and applies none (src/DotLLM.Cpu/Kernels/RoPE.md:303); the "llama3" rule here is
 the one published with the Llama 3.1 checkpoints: wavelengths below P/high keep their
 frequency, above P/low are divided by ``factor``, and those between are blended linearly in
-P/wavelength.  Tables are computed once in float64 and rounded to float32.
+P/wavelength.  The "yarn" rule blends per index instead: with d(t) = rotary_dim ln(P / (2 pi t)) / (2 ln theta) the
+index whose wavelength makes t turns over the original length P, the indices from lo = max(floor(d(fast)), 0) to
+hi = min(ceil(d(slow)), rotary_dim - 1) are ramped linearly from their own frequency to frequency / factor, and cos
+and sin are multiplied by 0.1 ln(factor) + 1 (``rotary_magnitude``).  Tables are computed once in float64 and rounded
+to float32.
 """
 from __future__ import annotations
 
@@ -27,6 +31,13 @@ def rotary_frequencies(rotary_dim, theta, scaling=None):
     if not scaling:
         return freq
     kind = scaling.get("rope_type")
+    if kind == "yarn":
+        factor, orig = float(scaling["factor"]), float(scaling["original_max_position_embeddings"])
+        index_of = lambda turns: rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(index_of(float(scaling["fast_turns"]))), 0)
+        hi = min(math.ceil(index_of(float(scaling["slow_turns"]))), rotary_dim - 1)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return freq / factor * ramp + freq * (1.0 - ramp)
     if kind != "llama3":
         raise ConfigError(f"unsupported rotary scaling {kind!r}")
     factor = float(scaling["factor"])
@@ -37,6 +48,13 @@ def rotary_frequencies(rotary_dim, theta, scaling=None):
     smooth = (orig / wavelen - low) / (high - low)
     blended = (1.0 - smooth) * freq / factor + smooth * freq
     return np.where(wavelen < orig / high, freq, np.where(wavelen > orig / low, freq / factor, blended))
+
+
+def rotary_magnitude(scaling=None):
+    """The factor on cos and sin: 0.1 ln(factor) + 1 under "yarn" scaling, else 1."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 _TABLES: dict = {}
@@ -57,7 +75,8 @@ class RotaryEncoding(PositionEncoding):
         if key not in _TABLES:                      # layers with equal parameters share one table
             freq = rotary_frequencies(self.rotary_dim, params["theta"], scaling)
             angle = np.arange(self.max_positions, dtype=np.float64)[:, None] * freq[None, :]
-            _TABLES[key] = tuple(torch.from_numpy(f(angle).astype(np.float32)).to(runtime.device).contiguous()
+            grow = rotary_magnitude(scaling)
+            _TABLES[key] = tuple(torch.from_numpy((f(angle) * grow).astype(np.float32)).to(runtime.device).contiguous()
                                  for f in (np.cos, np.sin))
         self.cos, self.sin = _TABLES[key]
 
@@ -75,7 +94,10 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPositionEncoding(PositionEncoding):
-    """Queries and keys carry no position information."""
+    """Queries and keys carry no position information: a rotation of no channels, as far as the kernels go."""
+
+    def fused_rotary(self):
+        return None, None, 0
 
     def apply(self, q, k, positions):
         return None

@@ -89,8 +89,29 @@ def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
     return (y * gf * torch.sigmoid(gf)).reshape(T, n_heads * vdim).to(out_dtype)
 
 
-def route_topk(x, w_router, bias, top):
-    z = x.to(torch.float32) @ w_router.to(torch.float32).T
+def unary_activation(x, kind):
+    assert kind == "relu2"
+    return (torch.relu(x.to(torch.float32)) ** 2).to(x.dtype)
+
+
+def activated_linear(x, w, kind, resident=False):
+    return unary_activation(linear(x, w, torch.float32), kind).to(x.dtype)
+
+
+def softcap(values, cap):
+    values.copy_(cap * torch.tanh(values / cap))
+    return values
+
+
+def head_gate(o, gate, n_heads, width):
+    g = torch.sigmoid(gate.to(torch.float32))
+    o.copy_((o.to(torch.float32).reshape(o.shape[0], n_heads, width) * g[:, :, None]).reshape(o.shape).to(o.dtype))
+    return o
+
+
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False):
+    logits = x.to(torch.float32) @ w_router.to(torch.float32).T
+    z = logits[:, :experts] if experts is not None else logits
     if bias is not None:
         z = z + bias
     ids = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
@@ -100,23 +121,30 @@ def route_topk(x, w_router, bias, top):
         at = (z == best[:, None]).to(torch.int32).argmax(dim=-1)
         ids[:, j], vals[:, j] = at, best
         z = z.scatter(1, at[:, None], float("-inf"))
-    return ids, torch.softmax(vals, dim=-1)
+    weights = torch.sigmoid(vals) if scoring == "sigmoid" else torch.softmax(vals, dim=-1)
+    return (ids, weights, logits) if with_logits else (ids, weights)
 
 
-def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0):
+def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0, row_scale=None):
     T, top = ids.shape
-    rows = [gated_activation(x[t:t + 1].to(torch.float32) @ w_gate_up[int(ids[t, j])].to(torch.float32).T, kind, limit, alpha)[0]
+    act = (lambda y: unary_activation(y, kind)) if kind == "relu2" else (lambda y: gated_activation(y, kind, limit, alpha))
+    scale = (lambda t, j: float(row_scale[t, j])) if row_scale is not None else (lambda t, j: 1.0)
+    rows = [act((x[t:t + 1].to(torch.float32) * scale(t, j)) @ w_gate_up[int(ids[t, j])].to(torch.float32).T)[0]
             for t in range(T) for j in range(top)]
-    return torch.stack(rows).to(x.dtype) if rows else torch.zeros((0, w_gate_up.shape[1] // 2), dtype=x.dtype)
+    width = w_gate_up.shape[1] if kind == "relu2" else w_gate_up.shape[1] // 2
+    return torch.stack(rows).to(x.dtype) if rows else torch.zeros((0, width), dtype=x.dtype)
 
 
-def expert_down(h, ids, weights, w_down, addend=None):
+def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None):
     T, top = ids.shape
     out = torch.zeros((T, w_down.shape[1]), dtype=torch.float32, device=h.device)
     for t in range(T):
         for j in range(top):
-            out[t] += weights[t, j] * (w_down[int(ids[t, j])].to(torch.float32) @ h[t * top + j].to(torch.float32))
-    return out if addend is None else out + addend
+            w = 1.0 if weights is None else weights[t, j]
+            out[t] += w * (w_down[int(ids[t, j])].to(torch.float32) @ h[t * top + j].to(torch.float32))
+    if addend is None:
+        return out
+    return out + (addend if addend_gate is None else addend * torch.sigmoid(addend_gate[:, :1]))
 
 
 def linear_per_head(x, w):
@@ -130,22 +158,33 @@ def _rotate(x, cos, sin, positions, n_heads, head_dim, rotary_dim):
     t = x.shape[0]
     xf = x.to(torch.float32).reshape(t, n_heads, head_dim)
     c, s = cos[positions.long()], sin[positions.long()]
-    return plain_llama.apply_rope(xf, c, s).reshape(t, n_heads * head_dim)
+    if rotary_dim == head_dim:
+        return plain_llama.apply_rope(xf, c, s).reshape(t, n_heads * head_dim)
+    half = rotary_dim // 2                          # the first rotary_dim channels in pairs (i, i + half), the rest as they are
+    u, v = xf[..., :half], xf[..., half:rotary_dim]
+    c, s = c[:, None, :], s[:, None, :]
+    return torch.cat([u * c - v * s, u * s + v * c, xf[..., rotary_dim:]], dim=-1).reshape(t, n_heads * head_dim)
 
 
 def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table,
-                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True):
+                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True, value_dim=None, biases=None):
+    vd = value_dim or head_dim
+    qb, kb, vb = biases if biases is not None else (None, None, None)
+    if qb is not None:
+        q.copy_((q.to(torch.float32) + qb).to(q.dtype))
     if rotary_dim:
         q.copy_(_rotate(q, cos, sin, token_pos, n_heads, head_dim, rotary_dim).to(q.dtype))
     if not write_cache:
         return
-    kr = _rotate(k, cos, sin, token_pos, n_kv_heads, head_dim, rotary_dim).to(k.dtype) if rotary_dim else k
+    kf = k.to(torch.float32) + kb if kb is not None else k
+    vf = (v.to(torch.float32) + vb).to(v.dtype) if vb is not None else v
+    kr = _rotate(kf, cos, sin, token_pos, n_kv_heads, head_dim, rotary_dim).to(k.dtype) if rotary_dim else kf.to(k.dtype)
     for t in range(q.shape[0]):
         pos = int(token_pos[t])
         page = int(block_table[int(token_seq[t]), pos // PAGE])
         assert page >= 0
         k_pool[page, :, pos % PAGE, :] = kr[t].reshape(n_kv_heads, head_dim)
-        v_pool[page, :, :, pos % PAGE] = v[t].reshape(n_kv_heads, head_dim)
+        v_pool[page, :, :, pos % PAGE] = vf[t].reshape(n_kv_heads, vd)
 
 
 def gather_kv(k_pool, v_pool, pages, length):
@@ -159,10 +198,11 @@ def gather_kv(k_pool, v_pool, pages, length):
 
 
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None, score_hook=None):
-    if score_hook:
-        return _attention_with_hook(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
-                                    scale, window, score_hook)
+              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None):
+    vd = value_dim or head_dim
+    if score_hook or vd != head_dim or gate is not None:
+        return _attention_general(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
+                                  scale, window, score_hook, vd, gate)
     T = q.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
     for t in range(T):
@@ -182,11 +222,12 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
     return out.to(q.dtype)
 
 
-def _attention_with_hook(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim, scale,
-                         window, hook):
-    """Scores capped (softcap * tanh(s / softcap)) and then biased by slope * (key - query position)."""
+def _attention_general(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim, scale,
+                       window, hook, vd, gate):
+    """Scores capped (softcap * tanh(s / softcap)) and then biased by slope * (key - query position); values of
+    their own width; a head's output times sigmoid of its gate logit."""
     T = q.shape[0]
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
+    out = torch.empty((T, n_heads * vd), dtype=torch.float32, device=q.device)
     group = n_heads // n_kv_heads
     for t in range(T):
         pos = int(token_pos[t])
@@ -195,12 +236,13 @@ def _attention_with_hook(q, k_pool, v_pool, token_seq, token_pos, block_table, n
         for h in range(n_heads):
             qh = q[t, h * head_dim:(h + 1) * head_dim].to(torch.float32)
             s = (k[first:, h // group] @ qh) * scale
-            if hook.softcap > 0:
+            if hook and hook.softcap > 0:
                 s = hook.softcap * torch.tanh(s / hook.softcap)
-            if hook.slopes is not None:
+            if hook and hook.slopes is not None:
                 s = s + float(hook.slopes[h]) * (torch.arange(first, pos + 1, dtype=torch.float32) - pos)
             w = torch.softmax(s, dim=0)
-            out[t, h * head_dim:(h + 1) * head_dim] = w @ v[first:, h // group]
+            o = w @ v[first:, h // group]
+            out[t, h * vd:(h + 1) * vd] = o if gate is None else o * torch.sigmoid(gate[t, h].to(torch.float32))
     return out.to(q.dtype)
 
 
