@@ -43,7 +43,10 @@ def rotary_frequencies(rot):
 
 
 def rotate(x, positions, rot):
-    """x [T, heads, d]: the first rot.dims channels of every head are rotated in pairs (i, i + dims/2)."""
+    """x [T, heads, d]: the first rot.dims channels of every head are rotated in pairs (i, i + dims/2).  No ``rot``:
+    nothing is rotated."""
+    if not rot or not rot.get("dims"):
+        return x
     dims = int(rot["dims"])
     f, grow = rotary_frequencies(rot)
     a = torch.as_tensor(positions, dtype=F)[:, None] * f[None, :]              # [T, dims/2]
@@ -73,13 +76,13 @@ def attention_keys_values(h, w, pre, m, positions):
     T, G, d, dv = h.shape[0], m["kv_heads"], m["dim"], m["vdim"]
     k = (h @ w[pre + "k"].to(F).T + w[pre + "k.b"].to(F)).view(T, G, d)
     v = (h @ w[pre + "v"].to(F).T + w[pre + "v.b"].to(F)).view(T, G, dv)
-    return rotate(k, positions, m["rot"]), v
+    return rotate(k, positions, m.get("rot")), v
 
 
 def attention_mixer(h, w, pre, m, positions, keys_values):
     """``keys_values``: (k, v) of the layer whose cache this one reads (its own, or another layer's)."""
     T, H, d = h.shape[0], m["heads"], m["dim"]
-    q = rotate((h @ w[pre + "q"].to(F).T + w[pre + "q.b"].to(F)).view(T, H, d), positions, m["rot"])
+    q = rotate((h @ w[pre + "q"].to(F).T + w[pre + "q.b"].to(F)).view(T, H, d), positions, m.get("rot"))
     k, v = keys_values
     o = causal_softmax_attention(q, k, v, float(m["scale"]))
     gate = torch.sigmoid(h @ w[pre + "g"].to(F).T)                                # [T, H]

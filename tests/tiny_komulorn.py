@@ -100,3 +100,30 @@ def read_folder(folder):
 def random_tokens(n, vocab, seed):
     rng = random.Random(seed)
     return [rng.randrange(vocab) for _ in range(n)]
+
+
+def rescale(folder, factors):
+    """Multiply stored tensors by factors ({name: factor}) and write the folder's weights again (values stay exact
+    in the stored type when the factor is a power of two)."""
+    from dotllm_b200.weights.safetensors_io import SafetensorsFile, save_safetensors
+    path = folder / "model.safetensors"
+    with SafetensorsFile(path) as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    for name, factor in factors.items():
+        tensors[name] = (tensors[name].to(torch.float32) * factor).to(tensors[name].dtype)
+    save_safetensors(path, tensors, metadata={"format": "pt"})
+    return folder
+
+
+def sharp_folder(tmp_path, which, dtype=torch.float32, seed=0):
+    """A folder of ``which`` ("sharp", "sharp_shared") whose query and key projections are scaled up (x16, biases x4) so
+    that, with the configuration's large score scale, a query's softmax all but picks one key."""
+    folder = make_folder(tmp_path, which, seed=seed, dtype=dtype)
+    factors = {}
+    for i, layer in enumerate(CONFIGS[which]["layers"]):
+        factors[f"l{i}.mix.q"] = 16.0
+        factors[f"l{i}.mix.q.b"] = 4.0
+        if layer["mixer"].get("kv_from") is None:
+            factors[f"l{i}.mix.k"] = 16.0
+            factors[f"l{i}.mix.k.b"] = 4.0
+    return rescale(folder, factors)
