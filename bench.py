@@ -6,6 +6,7 @@
     python bench.py --workload staggered              # Model.generate while 64 requests end one by one (also --shape 1b)
     python bench.py --workload short-prompts          # time to the first token of single short prompts, eager and captured
     python bench.py --workload kubedra [--shape 1b]   # the Kubedra design beside a Llama of equal width and depth, and its kernels
+    python bench.py --workload komulorn [--shape 1b]  # the Komulorn design beside a Llama of equal width, heads and depth, and its kernels
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -127,12 +128,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra"],
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra", "komulorn"],
                     help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
                          "staggered: Model.generate on 64 prompts whose requests end five steps apart; "
                          "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens; "
                          "kubedra: prefill and decode of the Kubedra design at layer sizes of a real model beside a Llama of "
-                         "equal width and depth, and each of its kernels against its roofline")
+                         "equal width and depth, and each of its kernels against its roofline; "
+                         "komulorn: the same for the Komulorn design beside a Llama of equal width, heads and depth")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -164,6 +166,8 @@ def main():
 
     if args.workload == "kubedra":
         return kubedra_workload(args)
+    if args.workload == "komulorn":
+        return komulorn_workload(args)
     pk = peaks()
     shape_name, shape = SHAPES[args.shape]
     cfg_dict = dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"])
@@ -424,27 +428,23 @@ KUBEDRA_SIZES = {
 }
 
 
-def kubedra_workload(args):
-    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
-    Kubedra model at a real model's layer sizes, beside a four-layer Llama of the same width, head count and feed-forward
-    width; then every kernel of the new design alone against its roofline (bytes it must move over the measured copy
-    bandwidth, or arithmetic over the measured bf16 rate), beside the like kernel of the Llama path.  Random weights,
-    synthetic tokens, bfloat16, CUDA events, an L2 flush between the timed launches of a kernel."""
+def design_bench_tools(args):
+    """What the workloads that set a design beside a Llama of equal size share: the measured peaks, a timer of one call
+    (median of the repetitions after three warm-ups, the L2 flushed before each unless told otherwise), and the three
+    points of a model (a prompt of `prefill_tokens` through an eager step, decode steps of 8 and 64 sequences at a context
+    of 2,048 tokens through captured steps)."""
+    import types
     import numpy as np
     import torch
-    from dotllm_b200 import Model, StepEntry
-    from dotllm_b200.config import config_from_dict
-    from dotllm_b200.kernels import ops
+    from dotllm_b200 import StepEntry
     pk = peaks()
     hbm, tflops = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
-    sizes = ["1b", "8b"] if args.shape not in ("1b",) else ["1b"]
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     gen = torch.Generator().manual_seed(1)
     reps, T, ctx = max(3, args.repeats), args.prefill_tokens, 2048
     sampler = ClockSampler()
-
     def timed(fn, n=None, flushed=True):
         n = n or reps
         out = []
@@ -493,6 +493,25 @@ def kubedra_workload(args):
             for s in seqs:
                 cache.close_sequence(s)
         return res
+
+    return types.SimpleNamespace(pk=pk, hbm=hbm, tflops=tflops, dev=dev, reps=reps, T=T, ctx=ctx, sampler=sampler, timed=timed,
+                                 model_points=model_points)
+
+
+def kubedra_workload(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
+    Kubedra model at a real model's layer sizes, beside a four-layer Llama of the same width, head count and feed-forward
+    width; then every kernel of the new design alone against its roofline (bytes it must move over the measured copy
+    bandwidth, or arithmetic over the measured bf16 rate), beside the like kernel of the Llama path.  Random weights,
+    synthetic tokens, bfloat16, CUDA events, an L2 flush between the timed launches of a kernel."""
+    import torch
+    from dotllm_b200 import Model
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.kernels import ops
+    tools = design_bench_tools(args)
+    pk, hbm, tflops, dev, T, ctx, sampler, timed, model_points = (tools.pk, tools.hbm, tools.tflops, tools.dev, tools.T, tools.ctx,
+                                                                  tools.sampler, tools.timed, tools.model_points)
+    sizes = ["1b", "8b"] if args.shape not in ("1b",) else ["1b"]
 
     def kernel_table(z):
         """Each kernel alone: (microseconds, fraction of its roofline) at prefill (T rows) and decode (64 rows) sizes."""
@@ -582,6 +601,154 @@ def kubedra_workload(args):
                       "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
                       "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
                       "config": {"model": "Kubedra, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
+                                 "l2": "flushed between a kernel's timed launches"},
+                      "peaks": pk, "sizes": out}))
+    return 0
+
+
+KOMULORN_SIZES = {
+    # width, heads, key/value heads and head size of the Llama shape of the same name; four layers, the second and the fourth
+    # reading the keys and values of the layer before them; every layer with routed experts and a gated shared expert
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot=64, experts=16, top=2, expert_ff=2048, shared_ff=2048, ff=8192),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, rot=64, experts=32, top=4, expert_ff=2048, shared_ff=2048, ff=14336),
+    # keys narrower than values: every head laid out at the values' width (zeros behind the keys)
+    "8b-96-128": dict(width=4096, heads=32, kv_heads=8, dim=96, vdim=128, rot=32, experts=32, top=4, expert_ff=2048, shared_ff=2048,
+                      ff=14336),
+}
+
+
+def komulorn_workload(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
+    Komulorn model at a real model's layer sizes, beside a four-layer Llama of the same width, heads and head size (its
+    closest relative here: the same attention over the same paged cache, a dense feed-forward instead of experts); then the
+    kernels that the design adds or changes, each alone against its roofline (bytes it must move over the measured copy
+    bandwidth, or arithmetic over the measured bf16 rate), beside the like kernel of the Llama or the Kubedra path.  Random
+    weights, synthetic tokens, bfloat16, CUDA events, an L2 flush between the timed launches of a kernel."""
+    import torch
+    from dotllm_b200 import Model
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.engine.step import AttentionPlan
+    from dotllm_b200.kernels import ops
+    tools = design_bench_tools(args)
+    pk, hbm, tflops, dev, T, ctx, sampler, timed, model_points = (tools.pk, tools.hbm, tools.tflops, tools.dev, tools.T, tools.ctx,
+                                                                  tools.sampler, tools.timed, tools.model_points)
+    sizes = ["1b"] if args.shape == "1b" else ["1b", "8b", "8b-96-128"]
+    bf = torch.bfloat16
+
+    def kernel_table(z):
+        W, H, G, hd, rd, E, top, ff = z["width"], z["heads"], z["kv_heads"], max(z["dim"], z["vdim"]), z["rot"], z["experts"], z["top"], z["expert_ff"]
+        rows = {}
+
+        def row(name, fn, bytes_=0, flops=0):
+            us = timed(fn) * 1000.0
+            need = max(bytes_ / hbm, flops / tflops) * 1e6
+            rows[name] = {"us": round(us, 1), "roofline_us": round(need, 2), "frac": round(need / us, 4)}
+        pos_table = torch.arange(ctx + T + 8, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)))
+        cos_full, sin_full = torch.cos(pos_table).float().to(dev), torch.sin(pos_table).float().to(dev)
+        cos_part, sin_part = cos_full[:, :rd // 2].contiguous(), sin_full[:, :rd // 2].contiguous()
+        qw, kw = H * hd, G * hd
+        for label, n_seqs, new, start in (("prefill", 1, T, 0), ("decode", 64, 1, ctx)):
+            n = n_seqs * new
+            pages_per = (start + new + 63) // 64
+            k_pool = torch.randn(n_seqs * pages_per + 1, G, 64, hd, device=dev).to(bf)
+            v_pool = torch.randn(n_seqs * pages_per + 1, G, hd, 64, device=dev).to(bf)
+            table = torch.arange(n_seqs * pages_per, dtype=torch.int32, device=dev).reshape(n_seqs, pages_per)
+            seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(new)
+            pos = (torch.arange(new, dtype=torch.int32, device=dev) + start).repeat(n_seqs)
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+            plan = AttentionPlan(n_seqs, new, start + new, new == 1, i32([start] * n_seqs), i32([new] * n_seqs),
+                                 i32([new * b for b in range(n_seqs + 1)]), i32([start + new] * n_seqs), [start] * n_seqs, [new] * n_seqs)
+            y = torch.randn(n, qw + 2 * kw + H + (-H % 16), device=dev).to(bf)
+            q, k, v, g = y[:, :qw], y[:, qw:qw + kw], y[:, qw + kw:qw + 2 * kw], y[:, qw + 2 * kw:qw + 2 * kw + H]
+            biases = tuple(torch.randn(m, device=dev) for m in (qw, kw, kw))
+            moved = n * (2 * qw + 2 * kw) * 2                                     # q read and written, k and v read and written
+            row(f"rotation of a part of the head + biases + cache write {label}",
+                lambda: ops.rope_cache_write(q, k, v, cos_part, sin_part, rd, seq, pos, table, k_pool, v_pool, H, G, hd, biases=biases), bytes_=moved)
+            row(f"llama rotation + cache write {label}",
+                lambda: ops.rope_cache_write(q, k, v, cos_full, sin_full, hd, seq, pos, table, k_pool, v_pool, H, G, hd), bytes_=moved)
+            kv_bytes = n_seqs * (start + new) * 2 * kw * 2
+            att_flops = 4 * H * hd * (n_seqs * (new * start + new * (new + 1) // 2))
+            att_io = kv_bytes + n * 2 * qw * 2
+            row(f"attention + head gate {label}", lambda: ops.attention(q, k_pool, v_pool, seq, pos, table, H, G, hd, hd ** -0.5, plan=plan, gate=g),
+                bytes_=att_io + n * 2 * qw * 2, flops=att_flops)
+            row(f"llama attention {label}", lambda: ops.attention(q, k_pool, v_pool, seq, pos, table, H, G, hd, hd ** -0.5, plan=plan),
+                bytes_=att_io, flops=att_flops)
+            if new == 1:
+                row("rotation + biases + cache write, attention, gate: a decode step's three launches",
+                    lambda: ops.rope_cache_attention(q, k, v, cos_part, sin_part, rd, seq, pos, table, k_pool, v_pool, H, G, hd, hd ** -0.5,
+                                                     plan=plan, biases=biases, gate=g), bytes_=att_io + moved)
+                row("llama rotation, cache write and attention in one launch (decode)",
+                    lambda: ops.rope_cache_attention(q, k, v, cos_full, sin_full, hd, seq, pos, table, k_pool, v_pool, H, G, hd, hd ** -0.5,
+                                                     plan=plan), bytes_=att_io + moved)
+            del k_pool, v_pool
+            # experts: one product with the square of relu, the score on the rows that go in
+            x = torch.randn(n, W, device=dev).to(bf)
+            wr = torch.randn(E + 1, W, device=dev).to(bf)
+            wu, wd = (torch.randn(E, ff, W, device=dev) * 0.02).to(bf), (torch.randn(E, W, ff, device=dev) * 0.02).to(bf)
+            wgu = (torch.randn(E, 2 * ff, W, device=dev) * 0.02).to(bf)
+            ids, wts, zl = ops.route_topk(x, wr, None, top, scoring="sigmoid", experts=E, with_logits=True)
+            shared = torch.randn(n, W, device=dev)
+            used = min(E, n * top)
+            row(f"route_topk, sigmoid scores {label}", lambda: ops.route_topk(x, wr, None, top, scoring="sigmoid", experts=E),
+                bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
+            if ops.experts_grouped_takes(x, ids, wu, wd):
+                row(f"experts sorted on tensor cores {label}",
+                    lambda: ops.experts_grouped(x, ids, None, wu, wd, "relu2", addend=shared, row_scale=wts, addend_gate=zl[:, E:]),
+                    bytes_=used * 2 * ff * W * 2 + n * W * (2 + 4 + 4) + n * top * (W * 2 + ff * 4 + W * 8), flops=2 * n * top * 2 * ff * W)
+                row(f"kubedra experts (gate and up) sorted on tensor cores {label}",
+                    lambda: ops.experts_grouped(x, ids, wts, wgu, wd, "clamped_sigmoid", 7.0, 1.702, addend=shared),
+                    bytes_=used * 3 * ff * W * 2 + n * W * (2 + 4 + 4) + n * top * (W * 2 + ff * 4 + W * 8), flops=2 * n * top * 3 * ff * W)
+            else:
+                row(f"expert up, row by row {label}", lambda: ops.expert_gate_up(x, ids, wu, "relu2", row_scale=wts),
+                    bytes_=used * ff * W * 2 + n * W * 2 + n * top * ff * 2, flops=2 * n * top * ff * W)
+                h = ops.expert_gate_up(x, ids, wu, "relu2", row_scale=wts)
+                row(f"expert down, row by row {label}", lambda: ops.expert_down(h, ids, None, wd, addend=shared, addend_gate=zl[:, E:]),
+                    bytes_=used * ff * W * 2 + n * top * ff * 2 + n * W * 8, flops=2 * n * top * ff * W)
+                row(f"kubedra expert gate and up, row by row {label}", lambda: ops.expert_gate_up(x, ids, wgu, "clamped_sigmoid", 7.0, 1.702),
+                    bytes_=used * 2 * ff * W * 2 + n * W * 2 + n * top * ff * 2, flops=2 * n * top * 2 * ff * W)
+            # the shared expert's first product with its activation, beside the Llama path's gated product of the same width
+            ws, wl = (torch.randn(z["shared_ff"], W, device=dev) * 0.02).to(bf), (torch.randn(2 * z["shared_ff"], W, device=dev) * 0.02).to(bf)
+            row(f"shared expert: product + square of relu {label}", lambda: ops.activated_linear(x, ws, "relu2", resident=True),
+                bytes_=z["shared_ff"] * W * 2 + n * W * 2 + n * z["shared_ff"] * 2, flops=2 * n * z["shared_ff"] * W)
+            row(f"llama gated product of that width {label}", lambda: ops.gated_linear(x, wl, resident=True),
+                bytes_=2 * z["shared_ff"] * W * 2 + n * W * 2 + n * z["shared_ff"] * 2, flops=2 * n * 2 * z["shared_ff"] * W)
+            logits = torch.randn(n_seqs, 32000, device=dev)
+            row(f"cap on the logits {label}", lambda: ops.softcap(logits, 30.0), bytes_=n_seqs * 32000 * 8)
+            del wu, wd, wgu, ws, wl
+        return rows
+
+    out = {}
+    for name in sizes:
+        z = KOMULORN_SIZES[name]
+        vocab = 32000
+        mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                 "rot": {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+        moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+               "shared": {"ff": z["shared_ff"]}}
+        own = lambda: {"type": "attention", "mixer": dict(mixer), "mlp": moe}
+        reads = lambda j: {"type": "attention", "mixer": dict(mixer, kv_from=j), "mlp": moe}
+        kcfg = {"architecture": "Komulorn", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "logit_softcap": 30.0, "layers": [own(), reads(0), own(), reads(2)]}
+        lcfg = dict(LLAMA_31_8B, num_hidden_layers=4, hidden_size=z["width"], num_attention_heads=z["heads"],
+                    num_key_value_heads=z["kv_heads"], head_dim=max(z["dim"], z["vdim"]), intermediate_size=z["ff"], vocab_size=vocab,
+                    max_position_embeddings=8192, tie_word_embeddings=True)
+        point = {}
+        for label, cfg_dict in (("komulorn", kcfg), ("llama", lcfg)):
+            model = Model.random(config_from_dict(cfg_dict), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+            point[label] = model_points(model, vocab)
+            print(f"[bench] {name} {label}: {point[label]}", file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        if z["dim"] == z["vdim"]:
+            point["kernels"] = kernel_table(z)
+            for k, v in point["kernels"].items():
+                print(f"[bench] {name} {k}: {v}", file=sys.stderr, flush=True)
+        out[name] = point
+    first = out[sizes[0]]
+    print(json.dumps({"metric": "komulorn_decode_tokens_per_second", "value": first["komulorn"]["decode_b8_tok_s"], "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
+                      "config": {"model": "Komulorn, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
                                  "l2": "flushed between a kernel's timed launches"},
                       "peaks": pk, "sizes": out}))
     return 0

@@ -13,6 +13,15 @@ biases on the three projections (added in float32 by the kernel that rotates and
 sigmoid of its logit, before the output projection; the gate's rows ride the stacked product), and an execution
 that reads another execution's keys and values (the schedule's ``cache_of``: such a layer has no key and value
 projections, ``own_kv`` False).
+
+Keys and values of different widths on the tensor cores.  The tensor-core attention kernels take one width for keys
+and values (32, 64, 96 or 128).  In a bfloat16 run a mixer whose two widths differ (and fit) therefore lays every head out
+at the smallest such width W that holds both: the stacked matrix gets rows of zeros behind each head's own rows (a
+head's q, k and v then come out of the product W wide, the added channels exactly zero), the biases zeros in the same
+places, the cache is W wide on both sides, and the output projection gets columns of zeros where the added value
+channels arrive.  Zero key channels add nothing to a score and zero value channels give zero outputs that meet zero
+columns, so the result is the unpadded one; the rotation's pairs (i, i + rot/2) lie in a head's first channels and do
+not move.  A float32 run, and widths beyond 128, keep the true widths and run the generic kernel.
 """
 from __future__ import annotations
 
@@ -79,6 +88,27 @@ class AttentionMixer(Mixer):
         self.w_qkv = None
         self.w_o = None
         self.biases = None
+        # the width every head is laid out at (see the module's text); head_dim / value_dim stay the stored widths
+        self.lay_k, self.lay_v = self.head_dim, self.value_dim
+        if runtime.dtype == torch.bfloat16 and self.value_dim != self.head_dim:
+            fits = [w for w in self.TENSOR_CORE_WIDTHS if w >= max(self.head_dim, self.value_dim)]
+            if fits and self.n_heads // self.n_kv_heads <= 16:
+                self.lay_k = self.lay_v = fits[0]
+
+    TENSOR_CORE_WIDTHS = (32, 64, 96, 128)      # kernels.attention_fast.DECODE_HEAD_DIMS
+
+    @staticmethod
+    def _widen(t, heads, width, to, dim=0):
+        """``t`` with ``heads`` blocks of ``width`` along ``dim``, each block followed by zeros up to ``to``."""
+        if to == width:
+            return t
+        shape = list(t.shape)
+        shape[dim:dim + 1] = [heads, width]
+        pad = list(shape)
+        pad[dim + 1] = to - width
+        out = torch.cat([t.reshape(shape), torch.zeros(pad, dtype=t.dtype, device=t.device)], dim=dim + 1)
+        shape[dim:dim + 2] = [heads * to]
+        return out.reshape(shape)
 
     def weight_specs(self):
         h, n = self.hidden_size, self.names
@@ -98,7 +128,10 @@ class AttentionMixer(Mixer):
 
     def bind(self, tensors):
         n = self.names
-        rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
+        H, G, hd, vd, lk, lv = self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim, self.lay_k, self.lay_v
+        rows = [self._widen(tensors[n["q"]], H, hd, lk)]
+        if self.own_kv:
+            rows += [self._widen(tensors[n["k"]], G, hd, lk), self._widen(tensors[n["v"]], G, vd, lv)]
         if self.gate:
             rows.append(tensors[n["gate"]])
         if not self.plain:
@@ -107,18 +140,18 @@ class AttentionMixer(Mixer):
             if pad:
                 rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
         self.w_qkv = torch.cat(rows, dim=0).contiguous()
-        self.w_o = tensors[n["o"]].contiguous()
+        self.w_o = self._widen(tensors[n["o"]], H, vd, lv, dim=1).contiguous()
         if self.bias:
-            self.biases = (tensors[n["q_bias"]].contiguous(),
-                           tensors[n["k_bias"]].contiguous() if self.own_kv else None,
-                           tensors[n["v_bias"]].contiguous() if self.own_kv else None)
+            self.biases = (self._widen(tensors[n["q_bias"]], H, hd, lk).contiguous(),
+                           self._widen(tensors[n["k_bias"]], G, hd, lk).contiguous() if self.own_kv else None,
+                           self._widen(tensors[n["v_bias"]], G, vd, lv).contiguous() if self.own_kv else None)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
 
     def cache_need(self):
-        return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, window=self.window,
-                         v_dim=self.value_dim if self.value_dim != self.head_dim else None)
+        return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.lay_k, window=self.window,
+                         v_dim=self.lay_v if self.lay_v != self.lay_k else None)
 
     takes_scaled_rows = True                    # x goes straight into the Q/K/V product
 
@@ -129,7 +162,8 @@ class AttentionMixer(Mixer):
         if cache_view.writes != self.own_kv:
             raise ConfigError("attention: a layer without key and value projections must read another layer's cache "
                               "(and one with them keeps its own)")
-        qd, kvd, vw = self.q_dim, self.kv_dim, self.v_width
+        lk, lv = self.lay_k, self.lay_v
+        qd, kvd, vw = self.n_heads * lk, self.n_kv_heads * lk, self.n_kv_heads * lv
         y = ops.linear(x, self.w_qkv, resident=True)
         q, at = y[:, :qd], qd
         k = v = None
@@ -147,10 +181,10 @@ class AttentionMixer(Mixer):
             cos, sin, rotary_dim = fused
         a = ops.rope_cache_attention(q, k, v, cos, sin, rotary_dim, step.token_seq, step.token_pos,
                                      cache_view.block_table, cache_view.k, cache_view.v,
-                                     self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                     self.n_heads, self.n_kv_heads, lk, self.scale,
                                      int(self.window or 0), plan=step.attention_plan,
                                      score_hook=self.score_hook if self.score_hook else None,
-                                     value_dim=self.value_dim, biases=self.biases, gate=g)
+                                     value_dim=lv, biases=self.biases, gate=g)
         return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
     def forward(self, x, step, cache_view):

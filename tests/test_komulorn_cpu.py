@@ -213,3 +213,26 @@ def test_trace_replay_of_a_komulorn_folder(cpu_kernels, tmp_path):
     assert not (tmp_path / "out" / "1.f32").exists()
     assert torch.allclose(got0, ref[[0, 8]], atol=2e-4) and torch.allclose(got2, ref[[11]], atol=2e-4)
     assert not replayer.sequences
+
+
+@pytest.mark.parametrize("which,layer,width", [("A", 0, 64), ("D", 1, 96)])
+def test_heads_laid_out_at_a_common_width_give_the_same_logits(cpu_kernels, tmp_path, which, layer, width):
+    """A bfloat16 run lays keys and values of different widths out at one width that the tensor-core kernels take (zeros
+    behind each head's own channels).  The logits are those of the true widths, up to bfloat16's rounding."""
+    folder = tk.make_folder(tmp_path, which, dtype=torch.bfloat16)
+    cfg, w = tk.read_folder(folder)
+    model = load_into(DecoderModel(build_spec(load_config(folder)), Runtime(torch.bfloat16, torch.device("cpu"))), folder)
+    cache = model.new_cache(256)
+    need = model.cache_needs()[layer]
+    assert (need.key_width(), need.value_width()) == (width, width)
+    mixer = model.blocks[layer].mixer
+    assert (mixer.lay_k, mixer.lay_v) == (width, width) and mixer.w_o.shape[1] == mixer.n_heads * width
+    if which == "D":                     # twenty query heads on one key/value head are more than those kernels take: true widths
+        assert (model.blocks[0].mixer.lay_k, model.blocks[0].mixer.lay_v) == (8, 4)
+    tokens = tk.random_tokens(70, cfg["vocab"], 6)
+    ref = pk.forward(cfg, w, tokens).float()
+    s = cache.open_sequence()
+    out = torch.cat([run_step(model, cache, [StepEntry(s, tokens[:66], list(range(66)))]),
+                     run_step(model, cache, [StepEntry(s, tokens[66:], list(range(4)))])])
+    err = (out - ref).pow(2).mean(-1).sqrt() / ref.pow(2).mean(-1).sqrt()
+    assert float(err.median()) < 2e-2 and float(err.max()) < 0.5          # a router's near-tie may fall the other way in bfloat16

@@ -1,0 +1,404 @@
+"""Komulorn on the GPU against the plain implementation: each mechanism's kernel alone, whole prompts, portions,
+token-by-token decoding, unequal batches, slots and pages that are used again, far keys and shared caches that decide
+whole rows, long decoding over page borders, generation through the entry point, the replay program, the command line."""
+import copy
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs
+import plain_komulorn as pk
+import tiny_komulorn as tk
+from dotllm_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = [torch.float32, torch.bfloat16]
+# A row's rms error over the row's rms.  float32: summation order only, every row is held to the bound.
+# bfloat16: both sides read the same bfloat16 weights; the engine rounds activations to bfloat16 between parts.  A router
+# whose best scores nearly tie may choose the other expert in bfloat16, which changes that token's row and no other; so
+# nine rows in ten are held to HALF the bound, all but 3 % to the bound, and none may exceed LOOSE.
+REL = {torch.float32: 3e-5, torch.bfloat16: 4e-2}
+LOOSE = 0.6
+
+
+def row_errors(got, want):
+    g, w = got.double().cpu().reshape(-1, got.shape[-1]), want.double().cpu().reshape(-1, want.shape[-1])
+    return (g - w).pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-30)
+
+
+def rel_err(got, want):
+    return float(row_errors(got, want).max())
+
+
+def assert_rows(got, want, dtype, what=""):
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    err = row_errors(got, want)
+    if dtype == torch.float32:
+        assert float(err.max()) <= REL[dtype], f"{what}: a row's rms error is {float(err.max()):.3e} of its rms > {REL[dtype]:.1e}"
+        return
+    over = int((err > REL[dtype]).sum())
+    assert float(err.max()) <= LOOSE and over <= max(1, int(0.03 * err.numel())), \
+        f"{what}: {over} of {err.numel()} rows beyond {REL[dtype]:.1e}, the worst {float(err.max()):.3e}"
+    if err.numel() >= 10:
+        assert float(err.quantile(0.9)) <= REL[dtype] / 2, f"{what}: nine rows in ten should be within {REL[dtype] / 2:.1e}"
+
+
+@pytest.fixture(scope="module")
+def tmp(tmp_path_factory):
+    return tmp_path_factory.mktemp("komulorn")
+
+
+_loaded = {}
+
+
+def load_pair(tmp, which, dtype, seed=0):
+    from dotllm_b200 import Model
+    key = (which, dtype, seed)
+    if key not in _loaded:
+        folder = tk.sharp_folder(tmp, which, dtype=dtype, seed=seed) if which.startswith("sharp") else \
+            tk.make_folder(tmp, which, seed=seed, dtype=dtype)
+        cfg, weights = tk.read_folder(folder)
+        _loaded[key] = (Model.load(folder, dtype=dtype), cfg, weights, folder)
+    return _loaded[key]
+
+
+def g64(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+def close(got, want, dtype, tol32=2e-5, tol16=2e-2):
+    scale = float(want.double().abs().max().clamp_min(1e-6))
+    err = float((got.double().cpu() - want.double().cpu()).abs().max()) / scale
+    assert err <= (tol32 if dtype == torch.float32 else tol16), err
+
+
+# ------------------------------------------------------------------ mechanisms alone
+def paged(lens, nkv, hd, vd, dtype, seed):
+    """Pools of NaN with the keys and values of sequences of the given lengths on shuffled pages; the block table."""
+    pages = [(n + 63) // 64 for n in lens]
+    total = sum(pages) + 3
+    order = torch.randperm(total, generator=torch.Generator().manual_seed(seed)).tolist()
+    table = torch.full((len(lens), max(pages)), -1, dtype=torch.int32)
+    k_pool = torch.full((total, nkv, 64, hd), float("nan"), dtype=dtype)
+    v_pool = torch.full((total, nkv, vd, 64), float("nan"), dtype=dtype)
+    at = 0
+    for b, n in enumerate(pages):
+        for p in range(n):
+            table[b, p] = order[at]
+            at += 1
+    return k_pool, v_pool, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,vd,rd", [(6, 2, 24, 40, 16), (8, 2, 64, 64, 64), (3, 1, 10, 7, 6), (20, 1, 8, 4, 0),
+                                            (4, 2, 32, 96, 8), (4, 1, 16, 130, 16), (2, 2, 130, 2, 2)])
+def test_biased_rotation_cache_write_and_gated_attention_kernels(nh, nkv, hd, vd, rd, dtype):
+    """The kernel that adds biases, rotates a part of each head and writes keys and values of different widths to their
+    pages, then attention over those pages with a gate per head: three prompts of unequal lengths that cross pages in one
+    step, then a step of two portions and one decoded token, then one token each."""
+    starts = [0, 0, 0]
+    k_pool, v_pool, table = paged([151, 80, 131], nkv, hd, vd, dtype, 3)
+    rk_pool, rv_pool = k_pool.clone(), v_pool.clone()
+    pos_table = torch.arange(400, dtype=torch.float64)[:, None] * (50.0 ** (-torch.arange(max(rd, 2) // 2, dtype=torch.float64) / max(rd // 2, 1)))
+    cos, sin = (torch.cos(pos_table) * 1.07).float(), (torch.sin(pos_table) * 1.07).float()
+    biases = (g64(nh * hd, seed=1).float(), g64(nkv * hd, seed=2).float(), g64(nkv * vd, seed=3).float())
+    dev = lambda t: None if t is None else t.to(DEV)
+    gk, gv = k_pool.to(DEV), v_pool.to(DEV)
+    for round_, news in enumerate(([141, 70, 129], [9, 9, 1], [1, 1, 1])):
+        T = sum(news)
+        seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+        pos = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32)
+        width = nh * hd + nkv * hd + nkv * vd + nh
+        y = g64(T, width, seed=10 + round_).to(dtype)
+        want_y = y.clone()
+        q, k, v, g = (want_y[:, :nh * hd], want_y[:, nh * hd:nh * hd + nkv * hd],
+                      want_y[:, nh * hd + nkv * hd:nh * hd + nkv * hd + nkv * vd], want_y[:, -nh:])
+        kernel_refs.rope_cache_write(q, k, v, cos, sin, rd, seq, pos, table, rk_pool, rv_pool, nh, nkv, hd, value_dim=vd, biases=biases)
+        want = kernel_refs.attention(q, rk_pool, rv_pool, seq, pos, table, nh, nkv, hd, 0.3, value_dim=vd, gate=g)
+        gy = y.to(DEV)
+        gq, gkk, gvv, gg = (gy[:, :nh * hd], gy[:, nh * hd:nh * hd + nkv * hd],
+                            gy[:, nh * hd + nkv * hd:nh * hd + nkv * hd + nkv * vd], gy[:, -nh:])
+        got = ops.rope_cache_attention(gq, gkk, gvv, dev(cos) if rd else None, dev(sin) if rd else None, rd, dev(seq), dev(pos),
+                                       dev(table), gk, gv, nh, nkv, hd, 0.3, value_dim=vd, biases=tuple(dev(b) for b in biases),
+                                       gate=gg)
+        close(gq, q, dtype, 2e-6, 1e-2)                                          # the queries, biased and rotated in place
+        close(got, want, dtype, 2e-5, 2e-2)
+        held = ~torch.isnan(rk_pool)
+        assert torch.equal(torch.isnan(gk.cpu()), ~held)                        # nothing written beside the tokens' places
+        close(gk.cpu()[held], rk_pool[held], dtype, 2e-6, 1e-2)
+        close(gv.cpu()[~torch.isnan(rv_pool)], rv_pool[~torch.isnan(rv_pool)], dtype, 2e-6, 1e-2)
+        starts = [s + n for s, n in zip(starts, news)]
+    starts = [s - 1 for s in starts]                                             # the newest token of each sequence
+    # a layer that reads another's cache: queries only, nothing written
+    before = gk.clone()
+    y = g64(3, nh * hd + nh, seed=30).to(dtype).to(DEV)
+    ops.rope_cache_attention(y[:, :nh * hd], None, None, dev(cos) if rd else None, dev(sin) if rd else None, rd,
+                             dev(torch.tensor([0, 1, 2], dtype=torch.int32)), dev(torch.tensor(starts, dtype=torch.int32)), dev(table),
+                             gk, gv, nh, nkv, hd, 0.3, value_dim=vd, biases=(dev(biases[0]), None, None), gate=y[:, -nh:])
+    assert torch.equal(torch.nan_to_num(before), torch.nan_to_num(gk))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_gate_softcap_and_single_product_activation_kernels(dtype):
+    o, gate = g64(37, 6 * 40, seed=1).to(dtype), g64(37, 11, seed=2).to(dtype)
+    want = kernel_refs.head_gate(o.clone(), gate[:, 3:9], 6, 40)
+    got = ops.head_gate(o.to(DEV), gate.to(DEV)[:, 3:9], 6, 40)
+    close(got, want, dtype, 1e-6, 1e-2)
+    z = g64(5, 333, seed=3, scale=20.0).float()
+    close(ops.softcap(z.to(DEV), 12.5), 12.5 * torch.tanh(z.double() / 12.5), torch.float32, 1e-6)
+    for T in (3, 50, 300):
+        x, w = g64(T, 72, seed=4).to(dtype), g64(40, 72, seed=5, scale=0.2).to(dtype)
+        want = torch.relu(x.double() @ w.double().T) ** 2
+        close(ops.activated_linear(x.to(DEV), w.to(DEV), "relu2"), want, dtype, 2e-5, 2e-2)
+        close(ops.unary_activation(x.to(DEV)[:, 8:40], "relu2"), torch.relu(x.double()[:, 8:40]) ** 2, dtype, 1e-6, 1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,K,ff,E,top", [(7, 72, 40, 6, 2), (1, 52, 20, 3, 3), (40, 96, 56, 5, 1), (200, 64, 72, 4, 2)])
+def test_router_and_experts_with_the_weight_on_the_input(T, K, ff, E, top, dtype):
+    """Sigmoid scores that are not renormalised, ties to the lower index, the score on the expert's input, the square of
+    relu on one product, and a shared branch gated per token: row by row, and (bfloat16, enough rows) sorted into tiles."""
+    x = g64(T, K, seed=1).to(dtype)
+    wr = g64(E + 1, K, seed=2, scale=0.3).to(dtype)
+    if E > 2:
+        wr[2] = wr[0]                                                           # a tie in every row
+    up, down = g64(E, ff, K, seed=3, scale=0.2).to(dtype), g64(E, K, ff, seed=4, scale=0.2).to(dtype)
+    shared = g64(T, K, seed=5).float()
+    ids, weights, z = ops.route_topk(x.to(DEV), wr.to(DEV), None, top, scoring="sigmoid", experts=E, with_logits=True)
+    zz = x.double() @ wr.double().T
+    close(z, zz, dtype, 1e-5, 1e-5 if dtype == torch.float32 else 2e-2)
+    s = torch.sigmoid(z.double().cpu()[:, :E])                                  # the choice is held to the kernel's own logits
+    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :top]
+    assert torch.equal(ids.cpu().long(), order)
+    assert torch.allclose(weights.cpu().double(), torch.gather(s, 1, order), atol=1e-6)
+    want = torch.zeros(T, K, dtype=torch.float64)
+    for t in range(T):
+        for j in range(top):
+            e = int(order[t, j])
+            want[t] += torch.relu((float(weights[t, j]) * x[t].double()) @ up[e].double().T) ** 2 @ down[e].double().T
+    want += torch.sigmoid(z.double().cpu()[:, E:]) * shared.double()
+    h = ops.expert_gate_up(x.to(DEV), ids, up.to(DEV), "relu2", row_scale=weights)
+    got = ops.expert_down(h, ids, None, down.to(DEV), addend=shared.to(DEV), addend_gate=z[:, E:])
+    close(got, want, dtype, 3e-5, 3e-2)
+    if dtype == torch.bfloat16 and ops.experts_grouped_takes(x.to(DEV), ids, up.to(DEV), down.to(DEV)):
+        got = ops.experts_grouped(x.to(DEV), ids, None, up.to(DEV), down.to(DEV), "relu2", addend=shared.to(DEV),
+                                  row_scale=weights, addend_gate=z[:, E:])
+        close(got, want, dtype, 3e-5, 3e-2)
+    else:
+        assert dtype == torch.float32 or T * top < ops.GROUPED_MIN_ROWS
+
+
+# ------------------------------------------------------------------ whole models
+def run_cuts(model, tokens, cuts, want_all=True):
+    """Feed ``tokens`` to a fresh sequence in portions of the given sizes, the rest one by one; the logits of every token."""
+    from dotllm_b200.engine import StepEntry
+    cache = model.new_cache(64 * ((len(tokens) + 63) // 64 + 1))
+    cache.fill_free_pages(float("nan"))
+    seq = cache.open_sequence()
+    outs, at = [], 0
+    sizes = list(cuts)
+    while at < len(tokens):
+        n = min(sizes.pop(0) if sizes else 1, len(tokens) - at)
+        outs.append(model.step(cache, [StepEntry(seq, tokens[at:at + n], list(range(n)))]).clone())
+        at += n
+    cache.close_sequence(seq)
+    cache.check()
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+def test_whole_portions_and_decoding(tmp, which, dtype):
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    tokens = tk.random_tokens(150, cfg["vocab"], 7)
+    ref = pk.forward(cfg, w, tokens)
+    whole = run_cuts(model, tokens, [150])
+    assert_rows(whole, ref, dtype, "whole prompt")
+    for cuts in ([64, 2, 2, 62, 20], [1, 5, 17, 33, 64, 30], [129, 2], [140]):          # [140]: the last ten one by one
+        got = run_cuts(model, tokens, cuts)
+        assert_rows(got, ref, dtype, f"portions {cuts}")
+        if dtype == torch.float32:
+            assert rel_err(got, whole) < 1e-5, cuts
+    assert_rows(run_cuts(model, tokens[:40], []), ref[:40], dtype, "token by token from the first")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "B", "D"])
+def test_unequal_batches_slots_and_pages_used_again(tmp, which, dtype):
+    from dotllm_b200.engine import StepEntry
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    lens = [1, 70, 23, 131]
+    prompts = [tk.random_tokens(n + 12, cfg["vocab"], 20 + n) for n in lens]
+    refs = [pk.forward(cfg, w, p) for p in prompts]
+    cache = model.new_cache(64 * 8)
+    for round_ in range(2):                                          # the second time every slot and page has been used before
+        cache.fill_free_pages(float("nan"))
+        seqs = [cache.open_sequence() for _ in prompts]
+        order = list(range(len(prompts))) if round_ == 0 else [2, 0, 3, 1]
+        out = model.step(cache, [StepEntry(seqs[i], prompts[i][:lens[i]], [0, lens[i] - 1]) for i in order])
+        want = torch.cat([refs[i][[0, lens[i] - 1]] for i in order])
+        assert_rows(out, want, dtype, "a batch of unequal prompts")
+        live = list(order)
+        for t in range(12):
+            if t == 5:
+                gone = live.pop(1)                                   # a request ends early; its slot and pages go back ...
+                cache.close_sequence(seqs[gone])
+                cache.fill_free_pages(float("nan"))
+            out = model.step(cache, [StepEntry(seqs[i], [prompts[i][lens[i] + t]]) for i in live])
+            assert_rows(out, torch.stack([refs[i][lens[i] + t] for i in live]), dtype, f"decoding together, step {t}")
+        for i in live:
+            cache.close_sequence(seqs[i])
+        cache.check()
+    assert not cache.live
+
+
+def test_far_keys_decide_whole_rows(tmp):
+    """One attention layer whose scores are scaled until the softmax all but picks a single key.  The plain implementation
+    must differ visibly when the keys older than 100 tokens are hidden, when the frequencies are not rescaled, and when
+    the first token is hidden; the engine must agree with the right one: in a prompt that crosses pages, across a
+    portion's start, and when decoding goes on over page borders."""
+    dtype = torch.float32
+    model, cfg, w, _ = load_pair(tmp, "sharp", dtype)
+    tokens = tk.random_tokens(330, cfg["vocab"], 3)
+    ref = pk.forward(cfg, w, tokens)
+    rms = ref.pow(2).mean(-1).sqrt()
+    unscaled = copy.deepcopy(cfg)
+    del unscaled["layers"][0]["mixer"]["rot"]["scaling"]
+    assert int(((pk.forward(unscaled, w, tokens) - ref).pow(2).mean(-1).sqrt() / rms > 1e-2).sum()) >= 50
+    near = torch.stack([pk.forward(cfg, w, tokens[max(0, t - 99):t + 1])[-1] for t in range(200, 330, 5)])     # positions differ too
+    assert int(((near - ref[200:330:5]).pow(2).mean(-1).sqrt() / rms[200:330:5] > 1e-2).sum()) >= 10
+    for cuts in ([330], [63, 1, 1, 200], [128, 64, 2], [290]):
+        got = run_cuts(model, tokens, cuts)
+        assert rel_err(got, ref) < 1e-4, cuts
+    bf = load_pair(tmp, "sharp", torch.bfloat16)
+    got = run_cuts(bf[0], tokens, [300])
+    ref16 = pk.forward(bf[1], bf[2], tokens)
+    row_err = row_errors(got, ref16)
+    assert float(row_err.median()) < 3e-2 and int((row_err > 0.3).sum()) <= 3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_layer_that_reads_another_layers_cache(tmp, dtype):
+    """The second layer attends with its own queries over the first one's rotated keys and values.  The plain
+    implementation that gives it other keys differs visibly; the engine agrees with the right one in prompts, portions,
+    decoding and in a batch whose requests sit on mixed pages."""
+    from dotllm_b200.engine import StepEntry
+    model, cfg, w, _ = load_pair(tmp, "sharp_shared", dtype)
+    tokens = tk.random_tokens(200, cfg["vocab"], 4)
+    ref = pk.forward(cfg, w, tokens)
+    other = copy.deepcopy(cfg)
+    del other["layers"][1]["mixer"]["kv_from"]
+    w2 = dict(w, **{"l1.mix.k": w["l0.mix.k"].roll(1, 0), "l1.mix.k.b": w["l0.mix.k.b"], "l1.mix.v": w["l0.mix.v"],
+                    "l1.mix.v.b": w["l0.mix.v.b"]})
+    assert float(row_errors(pk.forward(other, w2, tokens), ref).median()) > 1e-2
+    for cuts in ([200], [65, 2, 100], [180]):
+        got = run_cuts(model, tokens, cuts)
+        if dtype == torch.float32:
+            assert rel_err(got, ref) < 1e-4, cuts
+        else:
+            err = row_errors(got, ref)
+            assert float(err.median()) < 3e-2 and int((err > 0.3).sum()) <= 4, cuts
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_over_page_borders(tmp, dtype):
+    model, cfg, w, _ = load_pair(tmp, "A", dtype)
+    tokens = tk.random_tokens(330, cfg["vocab"], 5)
+    ref = pk.forward(cfg, w, tokens)
+    got = run_cuts(model, tokens, [30])                              # 300 tokens one by one, over five page borders
+    assert_rows(got, ref, dtype, "300 decoded tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
+    from dotllm_b200 import InferenceOptions
+    model, cfg, w, _ = load_pair(tmp, which, dtype)
+    prompts = [tk.random_tokens(n, cfg["vocab"], 60 + n) for n in (1, 9, 40, 70)]
+    n_new = 24
+    outs = model.generate(prompts, InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason.value == "length" and o.generated_token_count == n_new
+        ref = pk.forward(cfg, w, p + o.generated_token_ids)
+        spread = float(ref.std())
+        for i, tok in enumerate(o.generated_token_ids):              # teacher-forced: the plain arg-max, or within rounding of it
+            row = ref[len(p) - 1 + i]
+            assert int(row.argmax()) == tok or float(row.max() - row[tok]) <= (1e-4 if dtype == torch.float32 else 0.1) * spread, \
+                (i, tok, int(row.argmax()))
+    again = model.generate(prompts, InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))      # through captured steps now
+    alone = model.generate(prompts[2], InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    if dtype == torch.float32:
+        assert [o.generated_token_ids for o in again] == [o.generated_token_ids for o in outs]
+        assert alone.generated_token_ids == outs[2].generated_token_ids
+
+
+def test_decode_steps_replayed_from_graphs(tmp):
+    """Steps captured as graphs (exact batch size and the shared widths with idle rows) give the eager steps' logits."""
+    from dotllm_b200.engine import StepEntry
+    dtype = torch.float32
+    model, cfg, w, _ = load_pair(tmp, "A", dtype)
+    prompts = [tk.random_tokens(n + 10, cfg["vocab"], 80 + n) for n in (5, 66, 30)]
+    refs = [pk.forward(cfg, w, p) for p in prompts]
+    for graphs in (True, "lazy"):
+        cache = model.new_cache(64 * 6)
+        seqs = [cache.open_sequence() for _ in prompts]
+        model.step(cache, [StepEntry(s, p[:-10], []) for s, p in zip(seqs, prompts)])
+        for t in range(10):
+            out = model.step(cache, [StepEntry(s, [p[len(p) - 10 + t]]) for s, p in zip(seqs, prompts)], graphs=graphs)
+            assert_rows(out, torch.stack([r[len(r) - 10 + t] for r in refs]), dtype, f"graphs={graphs} step {t}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program_on_a_komulorn_folder(tmp_path, dtype):
+    tdtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    folder = tk.make_folder(tmp_path, "D", seed=2, dtype=tdtype)
+    cfg, w = tk.read_folder(folder)
+    a, b = tk.random_tokens(90, cfg["vocab"], 1), tk.random_tokens(30, cfg["vocab"], 2)
+    ra, rb = pk.forward(cfg, w, a), pk.forward(cfg, w, b)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:80], "want": [0, 79]}, {"id": "b", "tokens": b[:20], "want": []}], "end": []}]
+    for t in range(10):
+        steps.append({"step": t + 1, "entries": [{"id": "a", "tokens": [a[80 + t]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[20 + t]], "want": [0] if t % 2 else []}],
+                      "end": ["a", "b"] if t == 9 else []})
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out_dir),
+                           "--max-tokens", "256"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [x for s in steps for x in ("done", str(s["step"]))]
+    read = lambda n: torch.from_numpy(np.fromfile(out_dir / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+    assert_rows(read(0), ra[[0, 79]], tdtype, "prompt step")
+    for t in range(10):
+        want = [ra[80 + t]] + ([rb[20 + t]] if t % 2 else [])
+        assert_rows(read(t + 1), torch.stack(want), tdtype, f"decode step {t}")
+
+
+def test_command_line_makes_and_runs_a_komulorn_folder(tmp_path):
+    """`random` writes a folder from a configuration file, `run` generates from it: greedy tokens are the plain
+    implementation's, a seeded sampled request gives the same tokens twice."""
+    import sys
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(tk.CONFIGS["C"]))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, "-m", "dotllm_b200", "random", str(cfg_path), str(folder), "--seed", "3", "--dtype", "float32"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr[-2000:]
+    cfg, w = tk.read_folder(folder)
+    prompt = tk.random_tokens(11, cfg["vocab"], 9)
+    run = lambda *extra: subprocess.run([sys.executable, "-m", "dotllm_b200", "run", str(folder), "-p", ",".join(map(str, prompt)),
+                                         "-n", "6", "--dtype", "float32", "--json", *extra], cwd=ROOT, capture_output=True, text=True,
+                                        timeout=600)
+    proc = run("-t", "0", "--stop-ids", "")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    tokens = json.loads(proc.stdout)["results"][0]["generated_token_ids"]
+    ref = pk.forward(cfg, w, prompt + tokens)
+    assert tokens == [int(ref[len(prompt) - 1 + i].argmax()) for i in range(6)]
+    a, b = run("-t", "0.9", "--top-k", "30", "-s", "5"), run("-t", "0.9", "--top-k", "30", "-s", "5")
+    assert a.returncode == 0 and json.loads(a.stdout)["results"][0]["generated_token_ids"] == \
+        json.loads(b.stdout)["results"][0]["generated_token_ids"]
