@@ -645,7 +645,9 @@ def komulorn_workload(args):
             rows[name] = {"us": round(us, 1), "roofline_us": round(need, 2), "frac": round(need / us, 4)}
         pos_table = torch.arange(ctx + T + 8, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)))
         cos_full, sin_full = torch.cos(pos_table).float().to(dev), torch.sin(pos_table).float().to(dev)
-        cos_part, sin_part = cos_full[:, :rd // 2].contiguous(), sin_full[:, :rd // 2].contiguous()
+        # the rotation of rd channels as the bfloat16 layout runs it: spread over the head, cos 1 and sin 0 behind the real columns
+        cos_part = torch.cat([cos_full[:, :rd // 2], torch.ones_like(cos_full[:, rd // 2:])], dim=1).contiguous()
+        sin_part = torch.cat([sin_full[:, :rd // 2], torch.zeros_like(sin_full[:, rd // 2:])], dim=1).contiguous()
         qw, kw = H * hd, G * hd
         for label, n_seqs, new, start in (("prefill", 1, T, 0), ("decode", 64, 1, ctx)):
             n = n_seqs * new
@@ -663,7 +665,7 @@ def komulorn_workload(args):
             biases = tuple(torch.randn(m, device=dev) for m in (qw, kw, kw))
             moved = n * (2 * qw + 2 * kw) * 2                                     # q read and written, k and v read and written
             row(f"rotation of a part of the head + biases + cache write {label}",
-                lambda: ops.rope_cache_write(q, k, v, cos_part, sin_part, rd, seq, pos, table, k_pool, v_pool, H, G, hd, biases=biases), bytes_=moved)
+                lambda: ops.rope_cache_write(q, k, v, cos_part, sin_part, hd, seq, pos, table, k_pool, v_pool, H, G, hd, biases=biases), bytes_=moved)
             row(f"llama rotation + cache write {label}",
                 lambda: ops.rope_cache_write(q, k, v, cos_full, sin_full, hd, seq, pos, table, k_pool, v_pool, H, G, hd), bytes_=moved)
             kv_bytes = n_seqs * (start + new) * 2 * kw * 2
@@ -674,8 +676,8 @@ def komulorn_workload(args):
             row(f"llama attention {label}", lambda: ops.attention(q, k_pool, v_pool, seq, pos, table, H, G, hd, hd ** -0.5, plan=plan),
                 bytes_=att_io, flops=att_flops)
             if new == 1:
-                row("rotation + biases + cache write, attention, gate: a decode step's three launches",
-                    lambda: ops.rope_cache_attention(q, k, v, cos_part, sin_part, rd, seq, pos, table, k_pool, v_pool, H, G, hd, hd ** -0.5,
+                row("rotation + biases + cache write, attention and gate in one launch (decode)",
+                    lambda: ops.rope_cache_attention(q, k, v, cos_part, sin_part, hd, seq, pos, table, k_pool, v_pool, H, G, hd, hd ** -0.5,
                                                      plan=plan, biases=biases, gate=g), bytes_=att_io + moved)
                 row("llama rotation, cache write and attention in one launch (decode)",
                     lambda: ops.rope_cache_attention(q, k, v, cos_full, sin_full, hd, seq, pos, table, k_pool, v_pool, H, G, hd, hd ** -0.5,
@@ -683,7 +685,7 @@ def komulorn_workload(args):
             del k_pool, v_pool
             # experts: one product with the square of relu, the score on the rows that go in
             x = torch.randn(n, W, device=dev).to(bf)
-            wr = torch.randn(E + 1, W, device=dev).to(bf)
+            wr = torch.randn(E + 8, W, device=dev).to(bf)                       # the experts' rows, the shared expert's gate, rows of padding
             wu, wd = (torch.randn(E, ff, W, device=dev) * 0.02).to(bf), (torch.randn(E, W, ff, device=dev) * 0.02).to(bf)
             wgu = (torch.randn(E, 2 * ff, W, device=dev) * 0.02).to(bf)
             ids, wts, zl = ops.route_topk(x, wr, None, top, scoring="sigmoid", experts=E, with_logits=True)
@@ -693,7 +695,7 @@ def komulorn_workload(args):
                 bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
             if ops.experts_grouped_takes(x, ids, wu, wd):
                 row(f"experts sorted on tensor cores {label}",
-                    lambda: ops.experts_grouped(x, ids, None, wu, wd, "relu2", addend=shared, row_scale=wts, addend_gate=zl[:, E:]),
+                    lambda: ops.experts_grouped(x, ids, None, wu, wd, "relu2", addend=shared, row_scale=wts, addend_gate=zl[:, E:E + 1]),
                     bytes_=used * 2 * ff * W * 2 + n * W * (2 + 4 + 4) + n * top * (W * 2 + ff * 4 + W * 8), flops=2 * n * top * 2 * ff * W)
                 row(f"kubedra experts (gate and up) sorted on tensor cores {label}",
                     lambda: ops.experts_grouped(x, ids, wts, wgu, wd, "clamped_sigmoid", 7.0, 1.702, addend=shared),
@@ -702,7 +704,7 @@ def komulorn_workload(args):
                 row(f"expert up, row by row {label}", lambda: ops.expert_gate_up(x, ids, wu, "relu2", row_scale=wts),
                     bytes_=used * ff * W * 2 + n * W * 2 + n * top * ff * 2, flops=2 * n * top * ff * W)
                 h = ops.expert_gate_up(x, ids, wu, "relu2", row_scale=wts)
-                row(f"expert down, row by row {label}", lambda: ops.expert_down(h, ids, None, wd, addend=shared, addend_gate=zl[:, E:]),
+                row(f"expert down, row by row {label}", lambda: ops.expert_down(h, ids, None, wd, addend=shared, addend_gate=zl[:, E:E + 1]),
                     bytes_=used * ff * W * 2 + n * top * ff * 2 + n * W * 8, flops=2 * n * top * ff * W)
                 row(f"kubedra expert gate and up, row by row {label}", lambda: ops.expert_gate_up(x, ids, wgu, "clamped_sigmoid", 7.0, 1.702),
                     bytes_=used * 2 * ff * W * 2 + n * W * 2 + n * top * ff * 2, flops=2 * n * top * 2 * ff * W)

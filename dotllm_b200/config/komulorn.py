@@ -150,9 +150,9 @@ class KomulornConfig:
                 raise ConfigError(f"config.json: layers[{i}].mixer.kv_from = {j} must name an earlier layer with keys and "
                                   f"values of its own")
             a, b = layer.mixer, parsed[j].mixer
-            if (a.kv_heads, a.dim, a.vdim) != (b.kv_heads, b.dim, b.vdim):
-                raise ConfigError(f"config.json: layers[{i}] reads the keys and values of layers[{j}], whose key/value heads "
-                                  f"and sizes differ")
+            if (a.kv_heads, a.dim, a.vdim, a.rot_dims) != (b.kv_heads, b.dim, b.vdim, b.rot_dims):
+                raise ConfigError(f"config.json: layers[{i}] reads the keys and values of layers[{j}], whose key/value heads, "
+                                  f"sizes or rotated channels differ")
         eos = d.get("eos_token_id")
         eos = () if eos is None else tuple(int(t) for t in (eos if isinstance(eos, (list, tuple)) else [eos]))
         cfg = cls(_get(d, "vocab", int, "config"), _get(d, "width", int, "config"), _get(d.get("norm"), "eps", float, "norm"),

@@ -253,7 +253,12 @@ struct AdFresh {
     const float* cos_t;              // [table_rows, hd/2] (rotate != 0)
     const float* sin_t;
     int table_rows;
-    int rotate;                      // 0: no rotation (the mixer encoded positions itself)
+    int rotate;                      // 0: no rotation (the mixer encoded positions itself); else q is rotated, and k where given
+    const float* q_bias;             // [nh*hd], [nkv*hd], [nkv*hd] float32 or NULL: added to the projections before the rotation
+    const float* k_bias;
+    const float* v_bias;
+    const __nv_bfloat16* gate;       // one logit per (sequence, query head), rows gate_stride apart, or NULL: a head's output
+    int gate_stride;                 // is multiplied by sigmoid(logit) as it is written
 };
 
 // The same roundings as the rope kernels (no contraction), so that the fused and the separate way
@@ -277,6 +282,34 @@ __device__ __forceinline__ void ad_rotate8(uint4& x0, uint4& x1, const float* cs
     }
 }
 
+// The same with a bias (float32, eight values each) added to both pieces before the rotation.
+__device__ __forceinline__ void ad_rotate8_biased(uint4& x0, uint4& x1, const float* cs, const float* sn, const float* b0,
+                                                  const float* b1) {
+    const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&x0);
+    __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(&x1);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float f0 = __bfloat162float(a[e]) + b0[e], f1 = __bfloat162float(b[e]) + b1[e];
+        a[e] = __float2bfloat16_rn(ad_rot_lo(f0, f1, c[e], sv[e]));
+        b[e] = __float2bfloat16_rn(ad_rot_hi(f0, f1, c[e], sv[e]));
+    }
+}
+
+// x += bias for eight values (no rotation).
+__device__ __forceinline__ void ad_add8(uint4& x, const float* bias) {
+    __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = __float2bfloat16_rn(__bfloat162float(a[e]) + bias[e]);
+}
+
+__device__ __forceinline__ float ad_gate_factor(const __nv_bfloat16* gate_row, int head) {
+    return gate_row == nullptr ? 1.f : 1.f / (1.f + expf(-__bfloat162float(gate_row[head])));
+}
+
 // Merge the segments of one (sequence, KV head) that the cut spread over the blocks i0 .. i0 + n_seg - 1,
 // in block order, and write the group's heads.  The pair's first segment sits in its block's first or
 // last slot (`slot_first`), every other segment in its block's first.  Called by the consumer threads
@@ -285,7 +318,7 @@ __device__ __forceinline__ void ad_rotate8(uint4& x0, uint4& x1, const float* cs
 template <int HD, int BATCH>
 __device__ __forceinline__ void ad_merge_pair(__nv_bfloat16* __restrict__ out_pair, int group, int i0, int n_seg, int slot_first,
                                               const float* __restrict__ part_o, const float* __restrict__ part_ml, int tid,
-                                              int n_threads) {
+                                              int n_threads, const __nv_bfloat16* __restrict__ gate_pair) {
     constexpr int hd4 = HD / 4;
     for (int idx = tid; idx < group * hd4; idx += n_threads) {
         const int r = idx / hd4, d = (idx - r * hd4) * 4;
@@ -318,7 +351,7 @@ __device__ __forceinline__ void ad_merge_pair(__nv_bfloat16* __restrict__ out_pa
                 }
             }
         }
-        const float inv = 1.f / l;
+        const float inv = (1.f / l) * ad_gate_factor(gate_pair, r);
         __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
         __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
         uint2 packed;
@@ -457,15 +490,29 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     if (g < group) qf_lo[c] = *reinterpret_cast<const uint4*>(qb + (size_t)g * HD + c * 32 + t * 8);
                     if (WIDE && g + 8 < group) qf_hi[c] = *reinterpret_cast<const uint4*>(qb + (size_t)(g + 8) * HD + c * 32 + t * 8);
                 }
-                if (fresh.k != nullptr && fresh.rotate) {
+                // the biases of rows g and g+8 (read only where the row exists)
+                const float* qbias_lo = (fresh.q_bias != nullptr && g < group) ? fresh.q_bias + (size_t)(w.kvh * group + g) * HD : nullptr;
+                const float* qbias_hi = (WIDE && fresh.q_bias != nullptr && g + 8 < group) ? fresh.q_bias + (size_t)(w.kvh * group + g + 8) * HD : nullptr;
+                if (fresh.rotate) {
                     // slice c of the low half pairs with slice c + DC/2 of the high half, same lane
                     const int pos = min(w.len - 1, fresh.table_rows - 1);        // host-validated
                     const float* cs = fresh.cos_t + (size_t)pos * (HD / 2);
                     const float* sn = fresh.sin_t + (size_t)pos * (HD / 2);
 #pragma unroll
                     for (int c = 0; c < DC / 2; ++c) {
-                        ad_rotate8(qf_lo[c], qf_lo[c + DC / 2], cs + c * 32 + t * 8, sn + c * 32 + t * 8);
-                        if (WIDE) ad_rotate8(qf_hi[c], qf_hi[c + DC / 2], cs + c * 32 + t * 8, sn + c * 32 + t * 8);
+                        const int d0 = c * 32 + t * 8;
+                        if (qbias_lo != nullptr) ad_rotate8_biased(qf_lo[c], qf_lo[c + DC / 2], cs + d0, sn + d0, qbias_lo + d0, qbias_lo + HD / 2 + d0);
+                        else ad_rotate8(qf_lo[c], qf_lo[c + DC / 2], cs + d0, sn + d0);
+                        if (WIDE) {
+                            if (qbias_hi != nullptr) ad_rotate8_biased(qf_hi[c], qf_hi[c + DC / 2], cs + d0, sn + d0, qbias_hi + d0, qbias_hi + HD / 2 + d0);
+                            else ad_rotate8(qf_hi[c], qf_hi[c + DC / 2], cs + d0, sn + d0);
+                        }
+                    }
+                } else if (fresh.q_bias != nullptr) {
+#pragma unroll
+                    for (int c = 0; c < DC; ++c) {
+                        if (qbias_lo != nullptr) ad_add8(qf_lo[c], qbias_lo + c * 32 + t * 8);
+                        if (WIDE && qbias_hi != nullptr) ad_add8(qf_hi[c], qbias_hi + c * 32 + t * 8);
                     }
                 }
             }
@@ -483,6 +530,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
             const bool mine_new = i_new >= 0 && i_new < w.n_pages && (n0 + i_new) % n_stages == warp;
             uint2 kn_lo = make_uint2(0u, 0u), kn_hi = make_uint2(0u, 0u);
             float4 kn_c = make_float4(1.f, 1.f, 1.f, 1.f), kn_s = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 kn_blo = make_float4(0.f, 0.f, 0.f, 0.f), kn_bhi = make_float4(0.f, 0.f, 0.f, 0.f);   // the new key's biases
             __nv_bfloat16 vn_r[HD / 32];
             if (mine_new) {
                 const __nv_bfloat16* kn = fresh.k + (size_t)w.b * fresh.k_stride + (size_t)w.kvh * HD;
@@ -495,9 +543,18 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         kn_c = *reinterpret_cast<const float4*>(fresh.cos_t + (size_t)pos * (HD / 2) + lane * 4);
                         kn_s = *reinterpret_cast<const float4*>(fresh.sin_t + (size_t)pos * (HD / 2) + lane * 4);
                     }
+                    if (fresh.k_bias != nullptr) {
+                        const float* kb = fresh.k_bias + (size_t)w.kvh * HD;
+                        kn_blo = make_float4(kb[lane * 4], kb[lane * 4 + 1], kb[lane * 4 + 2], kb[lane * 4 + 3]);
+                        kn_bhi = make_float4(kb[HD / 2 + lane * 4], kb[HD / 2 + lane * 4 + 1], kb[HD / 2 + lane * 4 + 2], kb[HD / 2 + lane * 4 + 3]);
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < HD / 32; ++j) vn_r[j] = vn[lane + 32 * j];
+                for (int j = 0; j < HD / 32; ++j) {
+                    vn_r[j] = vn[lane + 32 * j];
+                    if (fresh.v_bias != nullptr)
+                        vn_r[j] = __float2bfloat16_rn(__bfloat162float(vn_r[j]) + fresh.v_bias[(size_t)w.kvh * HD + lane + 32 * j]);
+                }
             }
             for (int i = i_first; i < w.n_pages; i += n_stages) {
                 const int n = n0 + i;
@@ -521,7 +578,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         __nv_bfloat16 lo[4], hi[4];
                         *reinterpret_cast<uint2*>(lo) = kn_lo;
                         *reinterpret_cast<uint2*>(hi) = kn_hi;
-                        if (fresh.rotate) {
+                        if (fresh.k_bias != nullptr) {           // the bias in float32, one rounding behind the rotation (or behind the sum)
+                            const float cc[4] = {kn_c.x, kn_c.y, kn_c.z, kn_c.w}, ss[4] = {kn_s.x, kn_s.y, kn_s.z, kn_s.w};
+                            const float bl[4] = {kn_blo.x, kn_blo.y, kn_blo.z, kn_blo.w}, bh[4] = {kn_bhi.x, kn_bhi.y, kn_bhi.z, kn_bhi.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float f0 = __bfloat162float(lo[e]) + bl[e], f1 = __bfloat162float(hi[e]) + bh[e];
+                                lo[e] = __float2bfloat16_rn(fresh.rotate ? ad_rot_lo(f0, f1, cc[e], ss[e]) : f0);
+                                hi[e] = __float2bfloat16_rn(fresh.rotate ? ad_rot_hi(f0, f1, cc[e], ss[e]) : f1);
+                            }
+                        } else if (fresh.rotate) {
                             const float cc[4] = {kn_c.x, kn_c.y, kn_c.z, kn_c.w}, ss[4] = {kn_s.x, kn_s.y, kn_s.z, kn_s.w};
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
@@ -754,7 +820,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     }
                 }
                 if (w.whole) {
-                    const float inv = 1.f / l;
+                    const float inv = (1.f / l) * ad_gate_factor(fresh.gate != nullptr ? fresh.gate + (size_t)w.b * fresh.gate_stride : nullptr,
+                                                                 w.kvh * group + r);
                     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                     __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
                     uint2 packed;
@@ -788,7 +855,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 ad_consumer_sync(n_stages);                          // everyone has read the flag before it is written again
                 if (last)
                     ad_merge_pair<HD, WIDE ? 4 : 8>(out + (size_t)w.b * out_stride + (size_t)w.kvh * group * HD, group, i0, i1 - i0 + 1,
-                                      (w.pair_begin == i0 * cut.share) ? 0 : 1, part_o, part_ml, tid, 32 * n_stages);
+                                      (w.pair_begin == i0 * cut.share) ? 0 : 1, part_o, part_ml, tid, 32 * n_stages,
+                                      fresh.gate != nullptr ? fresh.gate + (size_t)w.b * fresh.gate_stride + w.kvh * group : nullptr);
             }
         }
     }
@@ -866,10 +934,12 @@ static int ad_dispatch(const void* q, int q_stride, void* out, int out_stride, v
         DL_REQUIRE(fresh.v != nullptr && fresh.k_stride % 4 == 0 && fresh.v_stride % 4 == 0 && ((uintptr_t)fresh.k % 8) == 0 &&
                        ((uintptr_t)fresh.v % 8) == 0 && fresh.k_stride >= nkv * hd && fresh.v_stride >= nkv * hd,
                    "attention_decode: the new keys and values must be 8-byte aligned rows of nkv*hd");
-        DL_REQUIRE(!fresh.rotate || ((hd == 64 || hd == 128) && fresh.cos_t && fresh.sin_t && fresh.table_rows > 0 &&
-                                     ((uintptr_t)fresh.cos_t % 16) == 0 && ((uintptr_t)fresh.sin_t % 16) == 0),
-                   "attention_decode: rotating inside the kernel takes head_dim 64 or 128 and 16-byte aligned tables");
     }
+    DL_REQUIRE(!fresh.rotate || ((hd == 64 || hd == 128) && fresh.cos_t && fresh.sin_t && fresh.table_rows > 0 &&
+                                 ((uintptr_t)fresh.cos_t % 16) == 0 && ((uintptr_t)fresh.sin_t % 16) == 0),
+               "attention_decode: rotating inside the kernel takes head_dim 64 or 128 and 16-byte aligned tables");
+    DL_REQUIRE(fresh.k != nullptr || (fresh.k_bias == nullptr && fresh.v_bias == nullptr), "attention_decode: biases of keys and values need the new keys and values");
+    DL_REQUIRE(fresh.gate == nullptr || fresh.gate_stride >= nh, "attention_decode: a row of gate logits holds one per query head");
     if (n_seqs == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool wide = nh / nkv > 8;
@@ -913,7 +983,7 @@ extern "C" int dl_attention_decode_fresh_bf16(const void* q, int q_stride, const
                                               float* part_ml, int part_slots, int* pair_counters, int n_counters, int* status,
                                               void* stream) {
     DL_REQUIRE(k_new != nullptr && v_new != nullptr, "attention_decode_fresh: needs the new keys and values");
-    AdFresh fresh;
+    AdFresh fresh = {};
     fresh.k = (const __nv_bfloat16*)k_new;
     fresh.k_stride = k_stride;
     fresh.v = (const __nv_bfloat16*)v_new;
@@ -922,6 +992,38 @@ extern "C" int dl_attention_decode_fresh_bf16(const void* q, int q_stride, const
     fresh.sin_t = sin_t;
     fresh.table_rows = table_rows;
     fresh.rotate = rotate;
+    return ad_dispatch(q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, bt_stride, n_seqs, nh, nkv,
+                       hd, scale, window, blocks, part_o, part_ml, part_slots, pair_counters, n_counters, fresh, status, stream);
+}
+
+// The same with the options of a mixer that biases its projections and gates its heads: q_bias [nh*hd], k_bias and v_bias
+// [nkv*hd] (float32, each NULL for none) are added before the rotation, with one rounding behind it as in
+// dl_rope_cache_write; gate (bfloat16, one logit per (sequence, query head), rows gate_stride apart, or NULL) multiplies
+// a head's output by sigmoid(logit) where it is written.  k_new and v_new may be NULL: a layer that reads another
+// layer's cache only biases and rotates its queries, and writes nothing to the pages.
+extern "C" int dl_attention_decode_gated_bf16(const void* q, int q_stride, const void* k_new, int k_stride, const void* v_new,
+                                              int v_stride, const float* cos_t, const float* sin_t, int table_rows, int rotate,
+                                              const float* q_bias, const float* k_bias, const float* v_bias, const void* gate,
+                                              int gate_stride, void* out, int out_stride, void* k_pool, void* v_pool, int n_pages,
+                                              const int32_t* seq_len, const int32_t* block_table, int bt_stride, int n_seqs,
+                                              int nh, int nkv, int hd, float scale, int window, int blocks, float* part_o,
+                                              float* part_ml, int part_slots, int* pair_counters, int n_counters, int* status,
+                                              void* stream) {
+    DL_REQUIRE((k_new == nullptr) == (v_new == nullptr), "attention_decode_gated: new keys and values come together");
+    AdFresh fresh = {};
+    fresh.k = (const __nv_bfloat16*)k_new;
+    fresh.k_stride = k_stride;
+    fresh.v = (const __nv_bfloat16*)v_new;
+    fresh.v_stride = v_stride;
+    fresh.cos_t = cos_t;
+    fresh.sin_t = sin_t;
+    fresh.table_rows = table_rows;
+    fresh.rotate = rotate;
+    fresh.q_bias = q_bias;
+    fresh.k_bias = k_bias;
+    fresh.v_bias = v_bias;
+    fresh.gate = (const __nv_bfloat16*)gate;
+    fresh.gate_stride = gate_stride;
     return ad_dispatch(q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, bt_stride, n_seqs, nh, nkv,
                        hd, scale, window, blocks, part_o, part_ml, part_slots, pair_counters, n_counters, fresh, status, stream);
 }

@@ -17,6 +17,8 @@ _library.register_signatures({
                                  _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_decode_fresh_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                        _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
+    "dl_attention_decode_gated_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I,
+                                       _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P, _P],
     "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
@@ -79,19 +81,29 @@ FRESH_ROTATE_HEAD_DIMS = (64, 128)   # head sizes whose rotation the decode kern
 
 
 def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads, n_kv_heads, head_dim,
-                 scale, window, plan):
+                 scale, window, plan, biases=None, gate=None):
     """A decode step with the new token handled inside the attention kernel (rotation of q and k,
-    cache write, attention): returns the output, or None when the sizes are not the kernel's."""
+    cache write, attention): returns the output, or None when the sizes are not the kernel's.
+    ``biases`` (q, k, v: float32 vectors or None) are added before the rotation and ``gate`` ([B, n_heads] logits of
+    q's dtype, a column view is fine) multiplies each head's output by its sigmoid, both inside the kernel; with them
+    k and v may be None (a layer that reads another's cache: only the queries are biased and rotated)."""
     group = n_heads // n_kv_heads
     if not (plan.all_single and q.shape[0] == plan.n_seqs and head_dim in DECODE_HEAD_DIMS and group <= 16
             and decode_fits(group, head_dim) and (rotary_dim == 0 or (rotary_dim == head_dim
                                                                       and head_dim in FRESH_ROTATE_HEAD_DIMS))):
         return None
     rows = lambda t: t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
-    qs, ks, vs = rows(q), rows(k), rows(v)
-    if q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or qs % 8 or ks % 4 or vs % 4 \
-            or q.data_ptr() % 16 or k.data_ptr() % 8 or v.data_ptr() % 8 or k.dtype != q.dtype or v.dtype != q.dtype \
-            or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+    extras = biases is not None or gate is not None
+    if k is None and not extras:
+        return None
+    qs = rows(q)
+    ks, vs = (rows(k), rows(v)) if k is not None else (0, 0)
+    if q.stride(1) != 1 or qs % 8 or q.data_ptr() % 16 or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        return None
+    if k is not None and (k.stride(1) != 1 or v.stride(1) != 1 or ks % 4 or vs % 4 or k.data_ptr() % 8 or v.data_ptr() % 8
+                          or k.dtype != q.dtype or v.dtype != q.dtype):
+        return None
+    if gate is not None and (gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape != (q.shape[0], n_heads)):
         return None
     if rotary_dim and (cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous()
                        or not sin.is_contiguous() or cos.shape != sin.shape or cos.shape[1] != head_dim // 2
@@ -101,6 +113,18 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
     out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
     part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
     counters = _pair_counters(q.device)
+    if extras:
+        qb, kb, vb = biases if biases is not None else (None, None, None)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        _library.call("dl_attention_decode_gated_bf16", q.data_ptr(), qs, ptr(k), ks, ptr(v), vs,
+                      cos.data_ptr() if rotary_dim else None, sin.data_ptr() if rotary_dim else None,
+                      cos.shape[0] if rotary_dim else 0, 1 if rotary_dim else 0, ptr(qb), ptr(kb) if k is not None else None,
+                      ptr(vb) if k is not None else None, ptr(gate), rows(gate) if gate is not None else 0,
+                      out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0],
+                      plan.seq_total.data_ptr(), block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
+                      scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots, counters.data_ptr(),
+                      counters.numel(), _library.status_word(q.device).data_ptr(), _library.current_stream())
+        return out
     _library.call("dl_attention_decode_fresh_bf16", q.data_ptr(), qs, k.data_ptr(), ks, v.data_ptr(), vs,
                   cos.data_ptr() if rotary_dim else None, sin.data_ptr() if rotary_dim else None,
                   cos.shape[0] if rotary_dim else 0, 1 if rotary_dim else 0, out.data_ptr(), out.stride(0),

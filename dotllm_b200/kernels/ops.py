@@ -420,14 +420,14 @@ def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, bl
                          value_dim=None, biases=None, gate=None):
     """``rope_cache_write`` followed by ``attention`` (same arguments, same result).  A bfloat16
     decode step (one new token per sequence) with a full-width rotation of head size 64 or 128, or
-    with no rotation, runs as one kernel that rotates q, puts the new keys and values into the
-    cache and attends; everything else runs the two kernels one after the other."""
-    plain = biases is None and (value_dim or head_dim) == head_dim
-    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None and not score_hook and plain:
+    with no rotation, runs as one kernel that adds the biases, rotates q, puts the new keys and values into the
+    cache, attends and gates the heads; everything else runs the kernels one after the other."""
+    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and not score_hook and (value_dim or head_dim) == head_dim \
+            and (k is not None or biases is not None or gate is not None):
         out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
-                                          n_kv_heads, head_dim, float(scale), int(window), plan)
+                                          n_kv_heads, head_dim, float(scale), int(window), plan, biases=biases, gate=gate)
         if out is not None:
-            return out if gate is None else head_gate(out, gate, n_heads, head_dim)
+            return out
     rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
                      n_heads, n_kv_heads, head_dim, write_cache=k is not None, value_dim=value_dim, biases=biases)
     return attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
@@ -760,14 +760,19 @@ def unary_activation(x, kind):
     return out
 
 
+ACTIVATED_TC_MIN_ROWS = 129     # fewer rows (a decode step) take the plain product's kernels and then the activation
+
+
 def activated_linear(x, w, kind, resident=False):
     """act(x W^T) for W [N, K] and an activation of one product (``UNGATED``); returns [T, N] in x's dtype.  Many bfloat16
-    rows: the tcgen05 product with the activation in its epilogue; otherwise the product and then the activation."""
+    rows (a prompt step): the tcgen05 product with the activation in its epilogue; otherwise the product (weight-streaming
+    for a few rows) and then the activation."""
     x = resolve(x) if isinstance(x, ScaledRows) else x
     _need_cuda(x, w)
     if kind not in UNGATED:
         raise KernelError(f"activated_linear: {kind!r} is no activation of one product; known: {sorted(UNGATED)}")
-    if x.dtype == torch.bfloat16 and w.dim() == 2 and x.dim() == 2 and x.shape[1] == w.shape[1] and gemm_tc.takes(x, w):
+    if x.dtype == torch.bfloat16 and w.dim() == 2 and x.dim() == 2 and x.shape[1] == w.shape[1] and gemm_tc.takes(x, w) \
+            and x.shape[0] >= ACTIVATED_TC_MIN_ROWS:
         return gemm_tc.run_activated(x, w, GATINGS[kind])
     return unary_activation(linear(x, w, resident=resident), kind)
 

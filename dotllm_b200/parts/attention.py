@@ -15,13 +15,22 @@ that reads another execution's keys and values (the schedule's ``cache_of``: suc
 projections, ``own_kv`` False).
 
 Keys and values of different widths on the tensor cores.  The tensor-core attention kernels take one width for keys
-and values (32, 64, 96 or 128).  In a bfloat16 run a mixer whose two widths differ (and fit) therefore lays every head out
-at the smallest such width W that holds both: the stacked matrix gets rows of zeros behind each head's own rows (a
+and values (32, 64, 96 or 128).  In a bfloat16 run a mixer with these options whose widths differ, or are equal and none of
+those four, therefore lays every head out at the smallest such width W that holds both (where one does): the stacked matrix gets rows of zeros behind each head's own rows (a
 head's q, k and v then come out of the product W wide, the added channels exactly zero), the biases zeros in the same
 places, the cache is W wide on both sides, and the output projection gets columns of zeros where the added value
 channels arrive.  Zero key channels add nothing to a score and zero value channels give zero outputs that meet zero
 columns, so the result is the unpadded one; the rotation's pairs (i, i + rot/2) lie in a head's first channels and do
 not move.  A float32 run, and widths beyond 128, keep the true widths and run the generic kernel.
+
+A rotation of a part of the head on the kernels that rotate whole heads.  The fused kernels (the decode attention that
+rotates the step's own token, the 16-byte rotation kernel) pair channel i with channel i + W/2.  A rotation of the first
+r < W channels pairs i with i + r/2.  Scores do not change when the channels of q and k are permuted alike, so in that
+layout the rows of the q and k projections (and their biases) are reordered once, when the weights are bound: the r/2 first
+members of the pairs to the head's channels 0 .., their partners to W/2 .., the unrotated channels behind each.  The
+rotary tables are widened to W/2 columns with cos 1 and sin 0 behind the r/2 real ones; a pair that meets those comes
+out as it went in, exactly.  What the cache holds are the keys in that order; a layer that reads another's cache
+orders its queries the same way (same widths and the same r).
 """
 from __future__ import annotations
 
@@ -90,12 +99,49 @@ class AttentionMixer(Mixer):
         self.biases = None
         # the width every head is laid out at (see the module's text); head_dim / value_dim stay the stored widths
         self.lay_k, self.lay_v = self.head_dim, self.value_dim
-        if runtime.dtype == torch.bfloat16 and self.value_dim != self.head_dim:
+        if runtime.dtype == torch.bfloat16 and not self.plain and \
+                (self.value_dim != self.head_dim or self.head_dim not in self.TENSOR_CORE_WIDTHS):
             fits = [w for w in self.TENSOR_CORE_WIDTHS if w >= max(self.head_dim, self.value_dim)]
             if fits and self.n_heads // self.n_kv_heads <= 16:
                 self.lay_k = self.lay_v = fits[0]
+        # a partial rotation spread over the whole head (see the module's text): fused_rotary() gives (cos, sin, r)
+        fused = self.position.fused_rotary()
+        rd = int(fused[2]) if fused is not None else 0
+        self.spread = bool(runtime.dtype == torch.bfloat16 and not self.plain and self.lay_k == self.lay_v
+                           and self.lay_k in self.TENSOR_CORE_WIDTHS and 0 < rd < self.lay_k)
+        self.rotation = None if fused is None else (self._wide_tables(fused[0], fused[1], rd, self.lay_k) + (self.lay_k,)
+                                                    if self.spread else fused)
+        self.spread_order = self._spread_order(rd, self.lay_k) if self.spread else None
 
     TENSOR_CORE_WIDTHS = (32, 64, 96, 128)      # kernels.attention_fast.DECODE_HEAD_DIMS
+
+    _WIDE_TABLES: dict = {}
+
+    @classmethod
+    def _wide_tables(cls, cos, sin, rd, width):
+        """The rotary tables with width/2 columns: the rd/2 real ones, then cos 1 and sin 0.  Layers with equal tables
+        share one pair."""
+        key = (cos.data_ptr() if cos.device.type != "meta" else id(cos), width, str(cos.device))
+        if key not in cls._WIDE_TABLES:
+            wide_cos = torch.ones((cos.shape[0], width // 2), dtype=cos.dtype, device=cos.device)
+            wide_sin = torch.zeros((sin.shape[0], width // 2), dtype=sin.dtype, device=sin.device)
+            wide_cos[:, :rd // 2] = cos
+            wide_sin[:, :rd // 2] = sin
+            cls._WIDE_TABLES[key] = (wide_cos.contiguous(), wide_sin.contiguous(), cos)     # cos kept: its address is the key
+        return cls._WIDE_TABLES[key][:2]
+
+    @staticmethod
+    def _spread_order(rd, width):
+        """new channel -> old channel of a head: pairs (i, i + rd/2) become pairs (i, i + width/2)."""
+        half, rest = rd // 2, (width - rd) // 2
+        return list(range(half)) + list(range(rd, rd + rest)) + list(range(half, rd)) + list(range(rd + rest, width))
+
+    def _reorder(self, t, heads):
+        """The rows (or entries) of ``t``, ``heads`` blocks of lay_k, in the spread order within each block."""
+        if self.spread_order is None:
+            return t
+        order = torch.tensor(self.spread_order, dtype=torch.long, device=t.device)
+        return t.reshape(heads, self.lay_k, *t.shape[1:])[:, order].reshape(t.shape)
 
     @staticmethod
     def _widen(t, heads, width, to, dim=0):
@@ -129,9 +175,9 @@ class AttentionMixer(Mixer):
     def bind(self, tensors):
         n = self.names
         H, G, hd, vd, lk, lv = self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim, self.lay_k, self.lay_v
-        rows = [self._widen(tensors[n["q"]], H, hd, lk)]
+        rows = [self._reorder(self._widen(tensors[n["q"]], H, hd, lk), H)]
         if self.own_kv:
-            rows += [self._widen(tensors[n["k"]], G, hd, lk), self._widen(tensors[n["v"]], G, vd, lv)]
+            rows += [self._reorder(self._widen(tensors[n["k"]], G, hd, lk), G), self._widen(tensors[n["v"]], G, vd, lv)]
         if self.gate:
             rows.append(tensors[n["gate"]])
         if not self.plain:
@@ -142,8 +188,8 @@ class AttentionMixer(Mixer):
         self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = self._widen(tensors[n["o"]], H, vd, lv, dim=1).contiguous()
         if self.bias:
-            self.biases = (self._widen(tensors[n["q_bias"]], H, hd, lk).contiguous(),
-                           self._widen(tensors[n["k_bias"]], G, hd, lk).contiguous() if self.own_kv else None,
+            self.biases = (self._reorder(self._widen(tensors[n["q_bias"]], H, hd, lk), H).contiguous(),
+                           self._reorder(self._widen(tensors[n["k_bias"]], G, hd, lk), G).contiguous() if self.own_kv else None,
                            self._widen(tensors[n["v_bias"]], G, vd, lv).contiguous() if self.own_kv else None)
 
     def weight_bytes(self):
@@ -170,7 +216,7 @@ class AttentionMixer(Mixer):
         if self.own_kv:
             k, v, at = y[:, at:at + kvd], y[:, at + kvd:at + kvd + vw], at + kvd + vw
         g = y[:, at:at + self.n_heads] if self.gate else None
-        fused = self.position.fused_rotary()
+        fused = self.rotation
         if fused is None:
             if self.biases is not None:
                 raise ConfigError("attention: biases need a position encoding that rides the cache-write kernel")

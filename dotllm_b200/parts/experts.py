@@ -31,6 +31,7 @@ class RoutedExperts(FeedForward):
     {e} and {m} for the expert's index and gate / up / down), ``router``, ``router_bias``, ``shared`` (with {m}),
     ``shared_gate``."""
 
+    ROUTER_ROW_STEP = 8
     NAMES = {"expert": "experts.{e}.{m}_proj.weight", "router": "router.weight", "router_bias": "router.bias",
              "shared": "shared_expert.{m}_proj.weight", "shared_gate": "shared_expert_gate.weight"}
 
@@ -102,7 +103,11 @@ class RoutedExperts(FeedForward):
                 self.ws_gate_up = tensors[name.format(m="up")].contiguous()
             self.ws_down = tensors[name.format(m="down")].contiguous()
             if self.shared_gate:                     # the gate's row behind the experts' rows: one product gives both
-                self.w_router = torch.cat([self.w_router, tensors[self.names["shared_gate"]]], dim=0).contiguous()
+                rows = [self.w_router, tensors[self.names["shared_gate"]]]
+                pad = -(self.n_experts + 1) % self.ROUTER_ROW_STEP       # rows of zeros: the library's product likes whole eights
+                if pad:
+                    rows.append(torch.zeros((pad, self.hidden_size), dtype=self.w_router.dtype, device=self.w_router.device))
+                self.w_router = torch.cat(rows, dim=0).contiguous()
 
     def weight_bytes(self):
         """Bytes a decode step of one token reads: the router, the chosen experts and the shared one."""
@@ -123,7 +128,7 @@ class RoutedExperts(FeedForward):
                 s = ops.activated_linear(x, self.ws_gate_up, self.activation, resident=True)
             shared = ops.linear(s, self.ws_down, out_dtype=torch.float32, resident=True)
             if self.shared_gate:
-                shared_gate = z[:, self.n_experts:]          # the logit of the row behind the experts' rows
+                shared_gate = z[:, self.n_experts:self.n_experts + 1]          # the logit of the row behind the experts' rows
         # the weight on the expert's input scales the rows that go in; nothing is left to weigh on the way out
         scale, weights = (weights, None) if self.weight_on == "input" else (None, weights)
         if ops.experts_grouped_takes(x, ids, self.w_gate_up, self.w_down):

@@ -402,3 +402,64 @@ def test_command_line_makes_and_runs_a_komulorn_folder(tmp_path):
     a, b = run("-t", "0.9", "--top-k", "30", "-s", "5"), run("-t", "0.9", "--top-k", "30", "-s", "5")
     assert a.returncode == 0 and json.loads(a.stdout)["results"][0]["generated_token_ids"] == \
         json.loads(b.stdout)["results"][0]["generated_token_ids"]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rotate", [(8, 2, 64, True), (32, 2, 128, True), (6, 2, 96, False), (4, 4, 32, False), (12, 1, 64, True)])
+def test_decode_attention_with_biases_and_gate_in_one_kernel(nh, nkv, hd, rotate):
+    """A decode step through the kernel that handles the step's own token itself: biases added before the rotation, the
+    new key and value put into the newest page, attention over pages that are cut between blocks, each head gated where
+    it is written.  Held to the plain references of the separate kernels; then a step of a layer that reads another's
+    cache (queries only), which must write nothing."""
+    from dotllm_b200.engine.step import AttentionPlan
+    dtype = torch.bfloat16
+    lens = [1, 700, 3000, 65]                                                    # after the step; the longest is cut between blocks
+    B = len(lens)
+    k_pool, v_pool, table = paged(lens, nkv, hd, hd, dtype, 5)
+    for b, n in enumerate(lens):                                                 # what the steps before left: n - 1 tokens
+        for j in range(n - 1):
+            page = int(table[b, j // 64])
+            k_pool[page, :, j % 64, :] = g64(nkv, hd, seed=1000 * b + j).to(dtype)
+            v_pool[page, :, :, j % 64] = g64(nkv, hd, seed=5000 * b + j).to(dtype)
+    ang = torch.arange(3100, dtype=torch.float64)[:, None] * (100.0 ** (-torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)))
+    cos, sin = (torch.cos(ang) * 1.1).float(), (torch.sin(ang) * 1.1).float()
+    cos[:, hd // 4:], sin[:, hd // 4:] = 1.0, 0.0                                # a rotation of half the head, spread over it
+    biases = (g64(nh * hd, seed=1).float(), g64(nkv * hd, seed=2).float(), g64(nkv * hd, seed=3).float())
+    seq = torch.arange(B, dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    dev = lambda t: None if t is None else t.to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    plan = AttentionPlan(B, 1, max(lens), True, i32([n - 1 for n in lens]), i32([1] * B), i32(list(range(B + 1))), i32(lens),
+                         [n - 1 for n in lens], [1] * B)
+    rd = hd if rotate else 0
+    y = g64(B, nh * hd + 2 * nkv * hd + nh + (-nh % 8), seed=7).to(dtype)
+    cut = lambda t: (t[:, :nh * hd], t[:, nh * hd:nh * hd + nkv * hd], t[:, nh * hd + nkv * hd:nh * hd + 2 * nkv * hd],
+                     t[:, nh * hd + 2 * nkv * hd:nh * hd + 2 * nkv * hd + nh])
+    want_y = y.clone()
+    q, k, v, g = cut(want_y)
+    rk, rv = k_pool.clone(), v_pool.clone()
+    kernel_refs.rope_cache_write(q, k, v, cos, sin, rd, seq, pos, table, rk, rv, nh, nkv, hd, biases=biases)
+    want = kernel_refs.attention(q, rk, rv, seq, pos, table, nh, nkv, hd, 0.2, gate=g)
+    gk, gv, gy = k_pool.to(DEV), v_pool.to(DEV), y.to(DEV)
+    gq, gkk, gvv, gg = cut(gy)
+    from dotllm_b200.kernels import attention_fast
+    got = attention_fast.decode_fresh(gq, gkk, gvv, dev(cos), dev(sin), rd, dev(table), gk, gv, nh, nkv, hd, 0.2, 0, plan,
+                                      biases=tuple(dev(b) for b in biases), gate=gg)
+    assert got is not None, "the fused kernel should take these sizes"
+    close(got, want, dtype, tol16=2e-2)
+    held = ~torch.isnan(rk)
+    assert torch.equal(torch.isnan(gk.cpu()), ~held)
+    close(gk.cpu()[held], rk[held], dtype, tol16=1e-2)
+    close(gv.cpu()[~torch.isnan(rv)], rv[~torch.isnan(rv)], dtype, tol16=1e-2)
+    assert torch.equal(gy.cpu(), y)                                              # the projections themselves are left as they came
+    # the same step for a layer that only has queries: the cache of the layer above, nothing written
+    y2 = g64(B, nh * hd + nh + (-nh % 8), seed=8).to(dtype)
+    w2 = y2.clone()
+    kernel_refs.rope_cache_write(w2[:, :nh * hd], None, None, cos, sin, rd, seq, pos, table, None, None, nh, nkv, hd,
+                                 write_cache=False, biases=(biases[0], None, None))
+    want2 = kernel_refs.attention(w2[:, :nh * hd], rk, rv, seq, pos, table, nh, nkv, hd, 0.3, gate=w2[:, nh * hd:nh * hd + nh])
+    before = gk.clone()
+    g2 = y2.to(DEV)
+    got2 = ops.rope_cache_attention(g2[:, :nh * hd], None, None, dev(cos), dev(sin), rd, dev(seq), dev(pos), dev(table), gk, gv,
+                                    nh, nkv, hd, 0.3, plan=plan, biases=(dev(biases[0]), None, None), gate=g2[:, nh * hd:nh * hd + nh])
+    close(got2, want2, dtype, tol16=2e-2)
+    assert torch.equal(torch.nan_to_num(before), torch.nan_to_num(gk))
