@@ -161,6 +161,10 @@ __device__ __forceinline__ void gs_epilogue(const float (&acc_in)[NT][4], TOut* 
                 if (g == 0 && tok0 + e < M) fuse.sumsq_out[(size_t)tile * 16 + tok0 + e] = ss[e];
             }
         } else {
+            if (fuse.gate_kind == GATE_RELU2) {              // an activation of the one product: relu(y)^2
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] = fmaxf(acc[e], 0.f) * fmaxf(acc[e], 0.f);
+            }
             const int row_lo = tile * 16 + g, row_hi = row_lo + 8;
             if (row_lo < N) {
                 if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_lo, acc[0]);
@@ -633,12 +637,14 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
 }
 
 // The gated product with another gating than SwiGLU (gating.cuh) in its epilogue; arguments as dl_gemm_skinny_bf16
-// with the gated flag set.
+// with the gated flag set.  With a `gate_kind` that is an activation of ONE product (relu^2) the gated flag is clear,
+// w is [N, K] and out = act(x W^T).
 extern "C" int dl_gemm_skinny_gated_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
                                          int out_stride, int M, int N, int K, int flags, int gate_kind, float limit, float alpha,
                                          float* partials, int partial_floats, int* counters, int n_counters, int* status,
                                          void* stream) {
-    DL_REQUIRE((flags & 1) == 1 && gate_kind >= 0 && gate_kind <= 2, "gemm_skinny_gated: a gated product with a known gating");
+    DL_REQUIRE(gate_kind >= 0 && gate_kind < GATE_KINDS && ((flags & 1) == 1) == dl_gate_is_gated(gate_kind),
+               "gemm_skinny_gated: a known gating, and the gated flag exactly where it reads two products");
     GsFuse fuse{};
     fuse.gate_kind = gate_kind, fuse.gate_limit = limit, fuse.gate_alpha = alpha;
     return gs_run(x, x_stride, w, out, out_dtype, out_stride, M, N, K, flags, partials, partial_floats, counters, n_counters,

@@ -125,6 +125,19 @@ def run_gating(x, w, gate_kind, limit, alpha, resident=False):
     return out
 
 
+def run_activated(x, w, kind, resident=False):
+    """act(x W^T) in x's dtype for W [N, K] and an activation of one product (``ops.UNGATED``) in the product's epilogue."""
+    M, K = x.shape
+    n_out = w.shape[0]
+    counters, partials, sms = _device_state(x.device)
+    x_stride = x.stride(0) if M > 1 else max(K, x.stride(0))
+    out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
+    _library.call("dl_gemm_skinny_gated_bf16", x.data_ptr(), x_stride, w.data_ptr(), out.data_ptr(), 1, n_out, M, n_out, K,
+                  2 if resident else 0, int(kind), 0.0, 0.0, partials.data_ptr(), partials.numel(),
+                  counters.data_ptr(), counters.numel(), _library.status_word(x.device).data_ptr(), _library.current_stream())
+    return out
+
+
 def scratch_need(M, N, K, fuse_swiglu=False, sms=148):
     """(partial floats, counters) the product of these sizes needs."""
     a, b = ctypes.c_int(0), ctypes.c_int(0)

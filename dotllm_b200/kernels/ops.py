@@ -765,8 +765,8 @@ ACTIVATED_TC_MIN_ROWS = 129     # fewer rows (a decode step) take the plain prod
 
 def activated_linear(x, w, kind, resident=False):
     """act(x W^T) for W [N, K] and an activation of one product (``UNGATED``); returns [T, N] in x's dtype.  Many bfloat16
-    rows (a prompt step): the tcgen05 product with the activation in its epilogue; otherwise the product (weight-streaming
-    for a few rows) and then the activation."""
+    rows (a prompt step): the tcgen05 product with the activation in its epilogue; a few rows (a decode step): the
+    weight-streaming product with it in its epilogue; otherwise the product and then the activation."""
     x = resolve(x) if isinstance(x, ScaledRows) else x
     _need_cuda(x, w)
     if kind not in UNGATED:
@@ -774,6 +774,9 @@ def activated_linear(x, w, kind, resident=False):
     if x.dtype == torch.bfloat16 and w.dim() == 2 and x.dim() == 2 and x.shape[1] == w.shape[1] and gemm_tc.takes(x, w) \
             and x.shape[0] >= ACTIVATED_TC_MIN_ROWS:
         return gemm_tc.run_activated(x, w, GATINGS[kind])
+    if x.dtype == torch.bfloat16 and w.dim() == 2 and x.dim() == 2 and x.shape[1] == w.shape[1] and 0 < x.shape[0] <= gemm_skinny.SKINNY_ROWS \
+            and gemm_skinny.takes(x, w):
+        return gemm_skinny.run_activated(x, w, GATINGS[kind], resident=resident)
     return unary_activation(linear(x, w, resident=resident), kind)
 
 
