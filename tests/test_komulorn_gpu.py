@@ -36,14 +36,14 @@ def rel_err(got, want):
     return float(row_errors(got, want).max())
 
 
-def assert_rows(got, want, dtype, what=""):
+def assert_rows(got, want, dtype, what="", loose=LOOSE):
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
     err = row_errors(got, want)
     if dtype == torch.float32:
         assert float(err.max()) <= REL[dtype], f"{what}: a row's rms error is {float(err.max()):.3e} of its rms > {REL[dtype]:.1e}"
         return
     over = int((err > REL[dtype]).sum())
-    assert float(err.max()) <= LOOSE and over <= max(1, int(0.03 * err.numel())), \
+    assert float(err.max()) <= loose and over <= max(1, int(0.03 * err.numel())), \
         f"{what}: {over} of {err.numel()} rows beyond {REL[dtype]:.1e}, the worst {float(err.max()):.3e}"
     if err.numel() >= 10:
         assert float(err.quantile(0.9)) <= REL[dtype] / 2, f"{what}: nine rows in ten should be within {REL[dtype] / 2:.1e}"
@@ -256,6 +256,57 @@ def test_unequal_batches_slots_and_pages_used_again(tmp, which, dtype):
             cache.close_sequence(seqs[i])
         cache.check()
     assert not cache.live
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_two_layers_at_a_real_models_widths(tmp, dtype):
+    """Width 1,024, heads of 128 channels with half of them rotated, experts of 512: the sizes at which the bfloat16 run
+    takes the tcgen05 attention and product kernels, the sorted experts and the fused decode attention.  (With two
+    layers and two of eight wide experts a token, a router's near-tie that falls the other way in bfloat16 changes most of
+    that token's row: such a row counts among the few that may exceed the bound, however far.)"""
+    model, cfg, w, _ = load_pair(tmp, "wide", dtype)
+    tokens = tk.random_tokens(330, cfg["vocab"], 11)
+    ref = pk.forward(cfg, w, tokens)
+    assert_rows(run_cuts(model, tokens, [300]), ref, dtype, "a prompt of 300 tokens and 30 decoded", loose=2.0)
+    assert_rows(run_cuts(model, tokens[:200], [130, 70]), ref[:200], dtype, "two portions", loose=2.0)
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Ten configurations that nobody chose (`tiny_komulorn.random_config`): a prompt and twenty decoded tokens, then a
+    batch of three unequal prompts (one of a single token) decoded together, eager and through captured steps, in both
+    dtypes.  In bfloat16 a row may be lost to a router's near-tie; the median row and all but a few must hold."""
+    import random
+    from dotllm_b200 import Model
+    from dotllm_b200.engine import StepEntry
+    rng = random.Random(seed)
+    cfg_dict = tk.random_config(rng)
+    n = rng.randrange(140, 420)
+    lens = [1, rng.randrange(2, 80), rng.randrange(80, 300)]
+    for dtype in DTYPES:
+        folder = tk.make_folder(tmp_path, f"random{seed}", dtype=dtype, cfg=cfg_dict)
+        cfg, w = tk.read_folder(folder)
+        model = Model.load(folder, dtype=dtype)
+        tokens = tk.random_tokens(n, cfg["vocab"], seed)
+        prompts = [tk.random_tokens(L + 8, cfg["vocab"], seed * 7 + L) for L in lens]
+        ref, refs = pk.forward(cfg, w, tokens), [pk.forward(cfg, w, p) for p in prompts]
+        got = [run_cuts(model, tokens, [n - 20])]
+        want = [ref]
+        cache = model.new_cache(64 * 12)
+        cache.fill_free_pages(float("nan"))
+        seqs = [cache.open_sequence() for _ in prompts]
+        got.append(model.step(cache, [StepEntry(q, p[:L], [L - 1]) for q, p, L in zip(seqs, prompts, lens)]).clone())
+        want.append(torch.stack([r[L - 1] for r, L in zip(refs, lens)]))
+        for t in range(8):
+            got.append(model.step(cache, [StepEntry(q, [p[L + t]]) for q, p, L in zip(seqs, prompts, lens)], graphs=t >= 4).clone())
+            want.append(torch.stack([r[L + t] for r, L in zip(refs, lens)]))
+        err = row_errors(torch.cat(got), torch.cat(want))
+        assert torch.isfinite(err).all()
+        if dtype == torch.float32:
+            assert float(err.max()) <= REL[dtype], (seed, float(err.max()))
+        else:
+            assert float(err.median()) <= REL[dtype] / 2 and float(err.max()) <= LOOSE and \
+                int((err > REL[dtype]).sum()) <= max(1, int(0.03 * err.numel())), (seed, float(err.median()), float(err.max()))
 
 
 def test_far_keys_decide_whole_rows(tmp):

@@ -77,8 +77,50 @@ CONFIGS = {
 SHARP = config(64, 120, 1e-5, [attention(4, 2, 16, 24, 6.0, rot(8, 10000.0, (4.0, 96, 8.0, 1.0)))])
 SHARP_SHARED = config(64, 120, 1e-5, [attention(4, 2, 16, 24, 6.0, rot(8, 10000.0, (4.0, 96, 8.0, 1.0))),
                                        attention(4, 2, 16, 24, 5.0, rot(8, 10000.0, (4.0, 96, 8.0, 1.0)), kv_from=0)])
+# Two layers at the widths of a real model's layers (the second on the first one's cache): heads of 128 channels, half of
+# them rotated, experts of 512.
+WIDE = config(1024, 1000, 1e-5,
+              [attention(8, 2, 128, 128, 128 ** -0.5, rot(64, 10000.0, (4.0, 2048, 32.0, 1.0)), mlp=moe(8, 2, 512, shared=512)),
+               attention(8, 2, 128, 128, 0.1, rot(64, 10000.0, (4.0, 2048, 32.0, 1.0)), kv_from=0, mlp=moe(8, 2, 512, shared=512))],
+              softcap=30.0)
+CONFIGS["wide"] = WIDE
 CONFIGS["sharp"] = SHARP
 CONFIGS["sharp_shared"] = SHARP_SHARED
+
+
+def random_config(rng):
+    """A configuration drawn from ``rng`` (a random.Random): two to five layers; widths that are and are not multiples of 8
+    or 64; one to four key/value heads with one to eight query heads each; key and value widths from 8 to 128, equal or
+    not; a rotation of no channel, a part of the head or all of it, rescaled or not; layers that read an earlier layer's
+    cache; two to 24 experts with one to four chosen, with and without a shared one; layers without a feed-forward."""
+    width = rng.choice([64, 96, 128, 160, 192, 256, 320, 100, 72])
+    layers, own = [], []
+    for i in range(rng.randrange(2, 6)):
+        mlp = None
+        if rng.random() > 0.15:
+            experts = rng.randrange(2, 25)
+            mlp = moe(experts, rng.randrange(1, min(4, experts) + 1), rng.choice([16, 24, 40, 56, 64, 96, 100, 136, 30]),
+                      shared=rng.choice([None, 16, 48, 128, 72]))
+        if own and rng.random() < 0.35:
+            j = rng.choice(own)
+            mixer = copy.deepcopy(layers[j]["mixer"])
+            mixer["scale"] = rng.choice([0.1, 0.2, 0.35])
+            mixer["kv_from"] = j
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+            continue
+        kv = rng.choice([1, 1, 2, 3, 4])
+        heads = kv * rng.choice([1, 2, 3, 4, 6, 8])
+        dim = rng.choice([8, 16, 24, 32, 40, 48, 64, 64, 80, 96, 128])
+        vdim = rng.choice([dim, dim, 8, 16, 24, 40, 64, 80, 96, 128, 20])
+        rd = rng.choice([0, dim, dim // 2 - (dim // 2) % 2, 2 * rng.randrange(1, dim // 2 + 1)])
+        rotation = None
+        if rd:
+            scaling = rng.choice([None, (rng.choice([2.0, 4.0, 8.0]), rng.choice([32, 64, 512, 4096]), rng.choice([4.0, 16.0, 32.0]),
+                                         rng.choice([0.5, 1.0, 2.0]))])
+            rotation = rot(rd, rng.choice([100.0, 10000.0, 500000.0]), scaling)
+        layers.append(attention(heads, kv, dim, vdim, rng.choice([0.1, 0.2, 0.35, dim ** -0.5]), rotation, mlp=mlp))
+        own.append(i)
+    return config(width, rng.randrange(100, 600), rng.choice([1e-5, 1e-6]), layers, softcap=rng.choice([None, 8.0, 30.0]))
 
 
 def make_folder(tmp_path, which, seed=0, dtype=torch.float32, cfg=None):
